@@ -1,0 +1,184 @@
+"""ctypes binding of libcute_b200.so: one Python function per C entry point.
+
+The signatures are those of include/cute_b200.h: plain integers, floats and
+device addresses.  Nothing here computes anything; without the shared library
+(or without a B200) every call fails loudly.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libcute_b200.so")
+
+OK = 0
+ERR_INVALID_ARGUMENT = -1
+ERR_MISALIGNED = -2
+ERR_UNSUPPORTED = -3
+ERR_NO_DEVICE = -4
+ERR_DEVICE_TIMEOUT = -5
+ERR_CUDA = -6
+ERR_NULL_POINTER = -7
+
+F16, BF16, F32, I32 = 0, 1, 2, 3
+
+EXPORTS = (
+    "cute_b200_status_string", "cute_b200_last_error", "cute_b200_init", "cute_b200_gemm_tn", "cute_b200_sgemm_nt",
+    "cute_b200_elementwise_add_f32", "cute_b200_launch", "cute_b200_launch_host", "cute_b200_upload",
+    "cute_b200_download", "cute_b200_free", "cute_b200_synchronize", "cute_b200_shard_rows",
+    "cute_b200_gemm_tn_shard", "cute_b200_device_status", "cute_b200_launch_count",
+)
+
+
+class GemmDesc(ctypes.Structure):
+    _fields_ = [("m", ctypes.c_int32), ("n", ctypes.c_int32), ("k", ctypes.c_int32), ("ab_dtype", ctypes.c_int32),
+                ("c_dtype", ctypes.c_int32), ("alpha", ctypes.c_float), ("beta", ctypes.c_float),
+                ("tile_n", ctypes.c_int32), ("cta_group", ctypes.c_int32), ("reserved", ctypes.c_int32 * 4)]
+
+
+class Arg(ctypes.Structure):
+    _fields_ = [("is_scalar", ctypes.c_int32), ("dtype", ctypes.c_int32), ("value", ctypes.c_uint64),
+                ("len", ctypes.c_uint64)]
+
+
+class LaunchCfg(ctypes.Structure):
+    _fields_ = [("grid", ctypes.c_uint32 * 3), ("block", ctypes.c_uint32 * 3), ("cluster", ctypes.c_uint32 * 3)]
+
+
+class CuteB200Error(RuntimeError):
+    """A non-zero status from the library; carries the code and its message."""
+
+    def __init__(self, status: int, message: str):
+        super().__init__(f"{status_string(status)}: {message}")
+        self.status = status
+        self.message = message
+
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """dlopen the library (no implicit build: see cute_rs_b200.build)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(f"{LIB_PATH} is missing: run `python -m cute_rs_b200.build` (needs nvcc)")
+    L = ctypes.CDLL(LIB_PATH)
+    i32, u64, f32, vp, cp = ctypes.c_int32, ctypes.c_uint64, ctypes.c_float, ctypes.c_void_p, ctypes.c_char_p
+    L.cute_b200_status_string.argtypes = [i32]
+    L.cute_b200_status_string.restype = cp
+    L.cute_b200_last_error.argtypes = []
+    L.cute_b200_last_error.restype = cp
+    L.cute_b200_init.argtypes = [i32]
+    L.cute_b200_gemm_tn.argtypes = [ctypes.POINTER(GemmDesc), u64, u64, u64, vp]
+    L.cute_b200_sgemm_nt.argtypes = [i32, i32, i32, f32, f32, u64, u64, u64, vp]
+    L.cute_b200_elementwise_add_f32.argtypes = [u64, u64, u64, u64, vp]
+    L.cute_b200_launch.argtypes = [cp, ctypes.POINTER(LaunchCfg), ctypes.POINTER(Arg), i32, vp]
+    L.cute_b200_launch_host.argtypes = [cp, ctypes.POINTER(LaunchCfg), ctypes.POINTER(Arg), i32,
+                                        ctypes.POINTER(ctypes.c_double)]
+    L.cute_b200_upload.argtypes = [vp, u64, ctypes.POINTER(u64)]
+    L.cute_b200_download.argtypes = [u64, vp, u64]
+    L.cute_b200_free.argtypes = [u64]
+    L.cute_b200_synchronize.argtypes = []
+    L.cute_b200_shard_rows.argtypes = [i32, i32, i32, ctypes.POINTER(i32), ctypes.POINTER(i32)]
+    L.cute_b200_gemm_tn_shard.argtypes = [ctypes.POINTER(GemmDesc), i32, i32, u64, u64, u64, i32, vp]
+    L.cute_b200_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint32 * 4)]
+    L.cute_b200_launch_count.argtypes = []
+    L.cute_b200_launch_count.restype = u64
+    for name in EXPORTS:
+        if name not in ("cute_b200_status_string", "cute_b200_last_error", "cute_b200_launch_count"):
+            getattr(L, name).restype = i32
+    _lib = L
+    return L
+
+
+def status_string(status: int) -> str:
+    return load().cute_b200_status_string(status).decode()
+
+
+def last_error() -> str:
+    return load().cute_b200_last_error().decode()
+
+
+def check(status: int) -> None:
+    if status != OK:
+        raise CuteB200Error(status, last_error())
+
+
+def init(device: int = 0) -> None:
+    check(load().cute_b200_init(device))
+
+
+def gemm_desc(m, n, k, ab_dtype, c_dtype, alpha=1.0, beta=0.0, tile_n=0, cta_group=0) -> GemmDesc:
+    return GemmDesc(m, n, k, ab_dtype, c_dtype, alpha, beta, tile_n, cta_group, (ctypes.c_int32 * 4)(0, 0, 0, 0))
+
+
+def gemm_tn(desc: GemmDesc, dA: int, dB: int, dC: int, stream: int = 0) -> None:
+    check(load().cute_b200_gemm_tn(ctypes.byref(desc), dA, dB, dC, stream))
+
+
+def gemm_tn_shard(desc: GemmDesc, world: int, rank: int, dA_shard: int, dB: int, dC_base: int, c_is_full: bool,
+                  stream: int = 0) -> None:
+    check(load().cute_b200_gemm_tn_shard(ctypes.byref(desc), world, rank, dA_shard, dB, dC_base, int(c_is_full),
+                                         stream))
+
+
+def shard_rows(m: int, world: int, rank: int) -> tuple[int, int]:
+    b, r = ctypes.c_int32(), ctypes.c_int32()
+    check(load().cute_b200_shard_rows(m, world, rank, ctypes.byref(b), ctypes.byref(r)))
+    return b.value, r.value
+
+
+def sgemm_nt(m, n, k, alpha, beta, dA: int, dB: int, dC: int, stream: int = 0) -> None:
+    check(load().cute_b200_sgemm_nt(m, n, k, alpha, beta, dA, dB, dC, stream))
+
+
+def elementwise_add_f32(dX: int, dY: int, dOut: int, n: int, stream: int = 0) -> None:
+    check(load().cute_b200_elementwise_add_f32(dX, dY, dOut, n, stream))
+
+
+def _cfg(grid, block, cluster=(1, 1, 1)) -> LaunchCfg:
+    return LaunchCfg((ctypes.c_uint32 * 3)(*grid), (ctypes.c_uint32 * 3)(*block), (ctypes.c_uint32 * 3)(*cluster))
+
+
+def launch(name: str, grid, block, args: list[Arg], cluster=(1, 1, 1), stream: int = 0) -> None:
+    arr = (Arg * len(args))(*args)
+    check(load().cute_b200_launch(name.encode(), ctypes.byref(_cfg(grid, block, cluster)), arr, len(args), stream))
+
+
+def launch_host(name: str, grid, block, args: list[Arg], cluster=(1, 1, 1)) -> float:
+    arr = (Arg * len(args))(*args)
+    sec = ctypes.c_double(0.0)
+    check(load().cute_b200_launch_host(name.encode(), ctypes.byref(_cfg(grid, block, cluster)), arr, len(args),
+                                       ctypes.byref(sec)))
+    return sec.value
+
+
+def upload(host_ptr: int, nbytes: int) -> int:
+    out = ctypes.c_uint64()
+    check(load().cute_b200_upload(host_ptr, nbytes, ctypes.byref(out)))
+    return out.value
+
+
+def download(device: int, host_ptr: int, nbytes: int) -> None:
+    check(load().cute_b200_download(device, host_ptr, nbytes))
+
+
+def free(device: int) -> None:
+    check(load().cute_b200_free(device))
+
+
+def synchronize() -> None:
+    check(load().cute_b200_synchronize())
+
+
+def device_status() -> tuple[int, int, int, int]:
+    out = (ctypes.c_uint32 * 4)()
+    check(load().cute_b200_device_status(ctypes.byref(out)))
+    return tuple(out)
+
+
+def launch_count() -> int:
+    return int(load().cute_b200_launch_count())

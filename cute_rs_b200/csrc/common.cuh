@@ -1,0 +1,56 @@
+// Shared host-side plumbing of libcute_b200: error reporting, per-device
+// state, launch accounting.  Internal; the public surface is include/cute_b200.h.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <string>
+
+#include "../../include/cute_b200.h"
+
+namespace cb {
+
+// Message of the calling thread's last failure; worded like the reference's
+// CudaError / check_launch messages (src/cuda.rs:532-546, src/sim/mod.rs:328-385).
+std::string &last_error();
+cute_b200_status fail(cute_b200_status code, const char *fmt, ...) __attribute__((format(printf, 2, 3)));
+cute_b200_status cuda_fail(cudaError_t err, const char *what);
+
+#define CB_CUDA(call)                                                  \
+    do {                                                               \
+        cudaError_t err__ = (call);                                    \
+        if (err__ != cudaSuccess) return ::cb::cuda_fail(err__, #call); \
+    } while (0)
+
+#define CB_TRY(call)                                   \
+    do {                                               \
+        cute_b200_status st__ = (call);                \
+        if (st__ != CUTE_B200_OK) return st__;         \
+    } while (0)
+
+// Per-device state created by cute_b200_init.
+struct DeviceState {
+    bool ready = false;
+    int sm_count = 0;
+    uint32_t *status_word = nullptr;  // 4 x u32 in device memory, zero when healthy
+};
+
+// State of the current device, initialising it on first use.
+cute_b200_status current_device(DeviceState **out);
+
+void count_launch(uint64_t n = 1);
+
+// Kernels, one translation unit each.
+cute_b200_status elementwise_add_f32(const float *x, const float *y, float *out, uint64_t n, cudaStream_t stream,
+                                     const DeviceState &dev);
+cute_b200_status sgemm_nt(int m, int n, int k, float alpha, float beta, const float *a, const float *b, float *c,
+                          cudaStream_t stream, const DeviceState &dev);
+cute_b200_status gemm_tn(const cute_b200_gemm_desc &desc, uint64_t a, uint64_t b, uint64_t c, cudaStream_t stream,
+                         const DeviceState &dev);
+cute_b200_status gemm_tn_init(const DeviceState &dev);
+cute_b200_status sgemm_nt_init(const DeviceState &dev);
+
+}  // namespace cb

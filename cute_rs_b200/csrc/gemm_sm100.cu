@@ -1,0 +1,598 @@
+// Tensor-core GEMM for sm_100a: C = alpha * A * B^T + beta * C with A (m, k)
+// and B (n, k) both K-major f16/bf16, f32 accumulation, C (m, n) row-major in
+// f32 or bf16.  Takes the place of the kernels the reference generates for
+// tensorop_gemm (examples/tensorop_gemm.rs:51-164) and runtime_gemm
+// (examples/runtime_gemm.rs:22-105), which are mma.sync.m16n8k16 kernels with
+// a cp.async ring; nothing of their structure is kept.
+//
+// Structure (one persistent CTA, or CTA pair, per SM):
+//   warp 0   TMA producer: cp.async.bulk.tensor.2d loads of a (128 x 64) A
+//            block and a (BN/pair x 64) B block per stage into 128-byte
+//            swizzled shared memory, completion counted on the stage's `full`
+//            mbarrier.
+//   warp 1   MMA issuer: one thread issues tcgen05.mma (M = 128 per CTA,
+//            N = BN, K = 16, four per stage) into a TMEM accumulator and
+//            releases the stage with tcgen05.commit on its `empty` mbarrier.
+//            Also owns the TMEM allocation.
+//   warps 2-5  epilogue: tcgen05.ld of the finished accumulator (each warp
+//            its own 32 TMEM lanes), alpha/beta, conversion, global stores.
+// The accumulator is double buffered in TMEM (2 x BN columns) so the epilogue
+// of tile i overlaps the main loop of tile i+1.
+//
+// With CTA_GROUP == 2 two CTAs of a cluster work on one 256-row tile: each
+// loads its own 128 rows of A and its own half of the B rows, the leader CTA
+// issues tcgen05.mma.cta_group::2 reading both shared memories, and each CTA
+// ends up with its 128 rows of the result in its own TMEM.  That halves the
+// B traffic per output.  The loads never use multicast.
+//
+// Every mbarrier wait has a time limit.  A waiter that gives up raises the
+// CTA's abort flag, writes a report to the device status word and all roles
+// fall through to the common teardown, so a protocol error ends the kernel
+// with an error code instead of hanging the GPU.
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "common.cuh"
+#include "ptx_sm100.cuh"
+
+namespace cb {
+namespace {
+
+constexpr int BM = 128;        // rows of C per CTA = TMEM lanes
+constexpr int BK = 64;         // k per stage: 64 x 2 B = one 128-byte swizzle row
+constexpr int UMMA_K = 16;     // k per tcgen05.mma for 16-bit inputs
+constexpr int NUM_THREADS = 192;
+constexpr uint32_t RING_BYTES = 192 * 1024;
+constexpr uint32_t BAR_BYTES = 256;
+constexpr uint64_t WAIT_LIMIT_NS = 4ull * 1000 * 1000 * 1000;
+
+// Report codes written to the status word.
+enum : uint32_t { WHERE_PRODUCER = 1, WHERE_MMA_FULL = 2, WHERE_MMA_TMEM = 3, WHERE_EPILOGUE = 4, WHERE_DRAIN = 5 };
+
+template <int CTA_GROUP, int BN>
+struct Cfg {
+    static constexpr int B_ROWS = BN / CTA_GROUP;  // B rows this CTA loads per stage
+    static constexpr uint32_t A_BYTES = BM * BK * 2;
+    static constexpr uint32_t B_BYTES = B_ROWS * BK * 2;
+    static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGES = RING_BYTES / STAGE_BYTES;
+    static constexpr uint32_t TMEM_COLS = 2 * BN;
+    static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + BAR_BYTES;
+    static_assert(STAGES >= 2 && STAGES <= 8, "ring depth");
+    static_assert(TMEM_COLS == 256 || TMEM_COLS == 512, "TMEM columns must be a power of two");
+};
+
+struct GemmParams {
+    void *C;
+    int M, N, K, ldc;
+    float alpha, beta;
+    uint32_t idesc;
+    int m_tiles, n_tiles, group_m;
+    int c_vec_ok;  // C base and row pitch allow 16-byte accesses
+    uint32_t *status;
+};
+
+// Shared-memory matrix descriptor of a K-major tile stored as 128-byte rows
+// with the 128B swizzle (what TMA writes with CU_TENSOR_MAP_SWIZZLE_128B):
+// start address >> 4, leading byte offset 1 (unused by swizzled K-major),
+// stride byte offset 1024 (eight rows), descriptor version 1, layout 2.
+__device__ __forceinline__ uint64_t sw128_desc(uint32_t saddr) {
+    return uint64_t((saddr & 0x3FFFFu) >> 4) | (uint64_t(1) << 16) | (uint64_t(1024 >> 4) << 32) |
+           (uint64_t(1) << 46) | (uint64_t(2) << 61);
+}
+
+__device__ __noinline__ void report_timeout(uint32_t *status, uint32_t where, uint32_t detail, uint32_t parity) {
+    if (atomicCAS(status, 0u, where) == 0u) {
+        status[1] = detail;
+        status[2] = blockIdx.x;
+        status[3] = parity;
+        __threadfence();
+    }
+}
+
+// Wait for phase `parity` of `bar`.  false = gave up (limit or CTA abort).
+__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
+                                         uint32_t *status, uint32_t where, uint32_t detail) {
+    if (ptx::mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = ptx::globaltimer_ns();
+    uint32_t spins = 0;
+    for (;;) {
+        if (ptx::mbar_try_wait(bar, parity)) return true;
+        if ((++spins & 255u) == 0u) {
+            if (*abort_flag) return false;
+            if (ptx::globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+                *abort_flag = 1u;
+                report_timeout(status, where, detail, parity);
+                return false;
+            }
+        }
+    }
+}
+
+struct TileCoord {
+    int tm, tn;
+};
+// Tiles are numbered so that `group_m` row tiles are walked before the column
+// advances: the CTAs running at one time then share a compact set of A and B
+// panels in L2.
+__device__ __forceinline__ TileCoord tile_coord(int t, const GemmParams &p) {
+    const int group_size = p.group_m * p.n_tiles;
+    const int g = t / group_size;
+    const int first = g * p.group_m;
+    const int gm = min(p.group_m, p.m_tiles - first);
+    const int r = t - g * group_size;
+    return {first + r % gm, r / gm};
+}
+
+template <bool C_BF16>
+__device__ __forceinline__ void store_chunk(const GemmParams &p, int row, int col0, const uint32_t (&v)[32],
+                                            bool plain) {
+    if (row >= p.M || col0 >= p.N) return;
+    const float alpha = p.alpha, beta = p.beta;
+    auto epi = [&](uint32_t acc_bits, float c_old) {
+        return __fadd_rn(__fmul_rn(alpha, __uint_as_float(acc_bits)), __fmul_rn(beta, c_old));
+    };
+    if constexpr (!C_BF16) {
+        float *crow = reinterpret_cast<float *>(p.C) + size_t(row) * p.ldc + col0;
+        if (p.c_vec_ok && col0 + 32 <= p.N) {
+#pragma unroll
+            for (int g = 0; g < 8; g++) {
+                float4 o;
+                if (plain) {
+                    o = make_float4(__uint_as_float(v[4 * g]), __uint_as_float(v[4 * g + 1]),
+                                    __uint_as_float(v[4 * g + 2]), __uint_as_float(v[4 * g + 3]));
+                } else {
+                    const float4 c = *reinterpret_cast<const float4 *>(crow + 4 * g);
+                    o = make_float4(epi(v[4 * g], c.x), epi(v[4 * g + 1], c.y), epi(v[4 * g + 2], c.z),
+                                    epi(v[4 * g + 3], c.w));
+                }
+                *reinterpret_cast<float4 *>(crow + 4 * g) = o;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; j++)
+                if (col0 + j < p.N) crow[j] = plain ? __uint_as_float(v[j]) : epi(v[j], crow[j]);
+        }
+    } else {
+        __nv_bfloat16 *crow = reinterpret_cast<__nv_bfloat16 *>(p.C) + size_t(row) * p.ldc + col0;
+        if (p.c_vec_ok && col0 + 32 <= p.N) {
+#pragma unroll
+            for (int g = 0; g < 4; g++) {
+                float f[8];
+                if (plain) {
+#pragma unroll
+                    for (int j = 0; j < 8; j++) f[j] = __uint_as_float(v[8 * g + j]);
+                } else {
+                    const uint4 c = *reinterpret_cast<const uint4 *>(crow + 8 * g);
+                    const uint32_t cw[4] = {c.x, c.y, c.z, c.w};
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        f[2 * j] = epi(v[8 * g + 2 * j], __uint_as_float(cw[j] << 16));
+                        f[2 * j + 1] = epi(v[8 * g + 2 * j + 1], __uint_as_float(cw[j] & 0xffff0000u));
+                    }
+                }
+                uint32_t w[4];
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+                    w[j] = *reinterpret_cast<const uint32_t *>(&h);
+                }
+                *reinterpret_cast<uint4 *>(crow + 8 * g) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; j++)
+                if (col0 + j < p.N) {
+                    const float r = plain ? __uint_as_float(v[j]) : epi(v[j], __bfloat162float(crow[j]));
+                    crow[j] = __float2bfloat16_rn(r);
+                }
+        }
+    }
+}
+
+template <int CTA_GROUP, int BN, bool C_BF16>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+    gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                   const GemmParams p) {
+    using C = Cfg<CTA_GROUP, BN>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = ptx::smem_u32(smem_raw);
+    const uint32_t ring = (raw + 1023u) & ~1023u;  // swizzle atoms need 1024-byte alignment
+    const uint32_t bars = ring + C::STAGES * C::STAGE_BYTES;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (C::STAGES + s); };
+    auto tfull_bar = [&](int a) { return bars + 8u * (2 * C::STAGES + a); };
+    auto tempty_bar = [&](int a) { return bars + 8u * (2 * C::STAGES + 2 + a); };
+    const uint32_t drain_bar = bars + 8u * (2 * C::STAGES + 4);
+    uint8_t *tail = smem_raw + (bars - raw) + 8u * (2 * C::STAGES + 5);
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(tail);
+    volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(tail + 4);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = CTA_GROUP == 1 ? 0u : ptx::cluster_ctarank();
+    const int cluster_id = blockIdx.x / CTA_GROUP;
+    const int num_clusters = gridDim.x / CTA_GROUP;
+    const int num_tiles = p.m_tiles * p.n_tiles;
+    const int k_blocks = (p.K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; s++) {
+            ptx::mbar_init(full_bar(s), 1);
+            ptx::mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            ptx::mbar_init(tfull_bar(a), 1);
+            ptx::mbar_init(tempty_bar(a), 4 * CTA_GROUP);  // one arrival per epilogue warp of the pair
+        }
+        ptx::mbar_init(drain_bar, 1);
+        *abort_flag = 0u;
+        ptx::fence_mbar_init();
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc<CTA_GROUP>(ptx::smem_u32(const_cast<uint32_t *>(tmem_slot)), C::TMEM_COLS);
+        ptx::tmem_relinquish<CTA_GROUP>();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    if constexpr (CTA_GROUP == 2) {  // the peer's barriers must exist before anything arrives on them
+        ptx::cluster_arrive();
+        ptx::cluster_wait();
+    }
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ producer
+        if (lane == 0) {
+            ptx::prefetch_tensormap(&tmA);
+            ptx::prefetch_tensormap(&tmB);
+            int s = 0;
+            uint32_t ph = 0;
+            uint32_t filled = 0, filled_parity = 0;  // per stage: was it filled, and in which phase
+            bool ok = true;
+            for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+                const TileCoord tc = tile_coord(t, p);
+                const int row_a = (tc.tm * CTA_GROUP + int(rank)) * BM;
+                const int row_b = tc.tn * BN + int(rank) * C::B_ROWS;
+                for (int kb = 0; kb < k_blocks; kb++) {
+                    if (!wait_bar(empty_bar(s), ph ^ 1u, abort_flag, p.status, WHERE_PRODUCER, uint32_t(s))) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t a_dst = ring + uint32_t(s) * C::STAGE_BYTES;
+                    const uint32_t b_dst = a_dst + C::A_BYTES;
+                    if constexpr (CTA_GROUP == 1) {
+                        ptx::mbar_arrive_expect_tx(full_bar(s), C::STAGE_BYTES);
+                        ptx::tma_load_2d(a_dst, &tmA, full_bar(s), kb * BK, row_a);
+                        ptx::tma_load_2d(b_dst, &tmB, full_bar(s), kb * BK, row_b);
+                    } else {
+                        // Both CTAs' bytes are counted on the leader's barrier,
+                        // which is the one the MMA issuer waits on.
+                        if (rank == 0) ptx::mbar_arrive_expect_tx(full_bar(s), 2 * C::STAGE_BYTES);
+                        const uint32_t leader_full = ptx::mapa(full_bar(s), 0);
+                        ptx::tma_load_2d_pair(a_dst, &tmA, leader_full, kb * BK, row_a);
+                        ptx::tma_load_2d_pair(b_dst, &tmB, leader_full, kb * BK, row_b);
+                    }
+                    filled |= 1u << s;
+                    filled_parity = (filled_parity & ~(1u << s)) | (ph << s);
+                    if (++s == C::STAGES) {
+                        s = 0;
+                        ph ^= 1u;
+                    }
+                }
+            }
+            if (!ok && (CTA_GROUP == 1 || rank == 0)) {
+                // Giving up: let this CTA's copies in flight land before the
+                // shared memory is handed back (bounded by the same limit).
+                for (int i = 0; i < C::STAGES; i++)
+                    if (filled & (1u << i)) {
+                        const uint64_t t0 = ptx::globaltimer_ns();
+                        while (!ptx::mbar_try_wait(full_bar(i), (filled_parity >> i) & 1u))
+                            if (ptx::globaltimer_ns() - t0 > WAIT_LIMIT_NS / 4) break;
+                    }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ---------------------------------------------------------- MMA issuer
+        if (lane == 0 && rank == 0 && k_blocks > 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true, issued = false;
+            int it = 0;
+            for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, it++) {
+                const int acc = it & 1;
+                const uint32_t aph = uint32_t(it >> 1) & 1u;
+                if (!wait_bar(tempty_bar(acc), aph ^ 1u, abort_flag, p.status, WHERE_MMA_TMEM, uint32_t(acc))) {
+                    ok = false;
+                    break;
+                }
+                ptx::tc_fence_after();
+                const uint32_t d_tmem = tmem_base + uint32_t(acc * BN);
+                for (int kb = 0; kb < k_blocks; kb++) {
+                    if (!wait_bar(full_bar(s), ph, abort_flag, p.status, WHERE_MMA_FULL, uint32_t(s))) {
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after();
+                    const uint32_t a_src = ring + uint32_t(s) * C::STAGE_BYTES;
+                    const uint64_t a_desc = sw128_desc(a_src), b_desc = sw128_desc(a_src + C::A_BYTES);
+#pragma unroll
+                    for (int j = 0; j < BK / UMMA_K; j++) {
+                        // 16 elements of k = 32 bytes = 2 units of the address field
+                        ptx::umma_f16<CTA_GROUP>(d_tmem, a_desc + 2u * j, b_desc + 2u * j, p.idesc,
+                                                 (kb > 0 || j > 0) ? 1u : 0u);
+                    }
+                    issued = true;
+                    ptx::umma_commit<CTA_GROUP>(empty_bar(s));
+                    if constexpr (CTA_GROUP == 2) ptx::umma_commit<CTA_GROUP>(ptx::mapa(empty_bar(s), 1));
+                    if (++s == C::STAGES) {
+                        s = 0;
+                        ph ^= 1u;
+                    }
+                }
+                if (!ok) break;
+                ptx::umma_commit<CTA_GROUP>(tfull_bar(acc));
+                if constexpr (CTA_GROUP == 2) ptx::umma_commit<CTA_GROUP>(ptx::mapa(tfull_bar(acc), 1));
+            }
+            if (!ok && issued) {
+                // Giving up: wait (bounded) until the tensor core is done with
+                // shared memory and TMEM before they are released.
+                ptx::umma_commit<CTA_GROUP>(drain_bar);
+                const uint64_t t0 = ptx::globaltimer_ns();
+                while (!ptx::mbar_try_wait(drain_bar, 0u))
+                    if (ptx::globaltimer_ns() - t0 > WAIT_LIMIT_NS / 4) break;
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------ epilogue
+        const uint32_t q = uint32_t(warp) & 3u;  // the TMEM lane quarter this warp may read
+        const bool plain = (p.alpha == 1.0f && p.beta == 0.0f);
+        bool ok = true;
+        int it = 0;
+        for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, it++) {
+            const TileCoord tc = tile_coord(t, p);
+            const int acc = it & 1;
+            const uint32_t aph = uint32_t(it >> 1) & 1u;
+            if (k_blocks > 0) {
+                if (!wait_bar(tfull_bar(acc), aph, abort_flag, p.status, WHERE_EPILOGUE, uint32_t(acc))) {
+                    ok = false;
+                    break;
+                }
+                ptx::tc_fence_after();
+            }
+            const int row = (tc.tm * CTA_GROUP + int(rank)) * BM + int(q) * 32 + lane;
+            const uint32_t taddr = tmem_base + ((q * 32u) << 16) + uint32_t(acc * BN);
+#pragma unroll 1
+            for (int chunk = 0; chunk < BN / 32; chunk++) {
+                uint32_t v[32];
+                if (k_blocks > 0) {
+                    ptx::tmem_ld_32x32(taddr + uint32_t(chunk * 32), v);
+                    ptx::tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) v[j] = 0u;
+                }
+                if (chunk == BN / 32 - 1 && k_blocks > 0) {
+                    // All of this warp's reads of the accumulator are done:
+                    // hand the TMEM buffer back before the last stores.
+                    ptx::tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if constexpr (CTA_GROUP == 1) ptx::mbar_arrive(tempty_bar(acc));
+                        else ptx::mbar_arrive_cluster(ptx::mapa(tempty_bar(acc), 0));
+                    }
+                }
+                store_chunk<C_BF16>(p, row, tc.tn * BN + chunk * 32, v, plain);
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    ptx::tc_fence_before();
+    __syncthreads();
+    if constexpr (CTA_GROUP == 2) {  // the peer may still arrive on our barriers or read our tiles
+        ptx::cluster_arrive();
+        ptx::cluster_wait();
+    }
+    if (warp == 1) ptx::tmem_dealloc<CTA_GROUP>(tmem_base, C::TMEM_COLS);
+}
+
+// out = alpha * 0 + beta * c (or 0 when C is write-only): the k == 0 case.
+template <bool C_BF16>
+__global__ void gemm_k0_kernel(void *C, size_t count, float alpha, float beta) {
+    const size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= count) return;
+    const bool plain = (alpha == 1.0f && beta == 0.0f);
+    if constexpr (C_BF16) {
+        __nv_bfloat16 *c = reinterpret_cast<__nv_bfloat16 *>(C);
+        const float r = plain ? 0.0f : __fadd_rn(__fmul_rn(alpha, 0.0f), __fmul_rn(beta, __bfloat162float(c[i])));
+        c[i] = __float2bfloat16_rn(r);
+    } else {
+        float *c = reinterpret_cast<float *>(C);
+        c[i] = plain ? 0.0f : __fadd_rn(__fmul_rn(alpha, 0.0f), __fmul_rn(beta, c[i]));
+    }
+}
+
+// ---------------------------------------------------------------------- host
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+cute_b200_status encode_fn(EncodeTiledFn *out) {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    static cudaError_t err = cudaSuccess;
+    std::call_once(once, [] {
+        void *sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        err = cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &sym, 12000, cudaEnableDefault, &q);
+        if (err == cudaSuccess && q == cudaDriverEntryPointSuccess) fn = reinterpret_cast<EncodeTiledFn>(sym);
+    });
+    if (!fn) return fail(CUTE_B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    *out = fn;
+    return CUTE_B200_OK;
+}
+
+// K-major (rows, k) 16-bit matrix, box (box_rows, 64), 128-byte swizzle,
+// out-of-range elements read as zero.
+cute_b200_status make_tensor_map(CUtensorMap *tm, uint64_t base, int dtype, int rows, int k, int box_rows) {
+    using Key = std::tuple<uint64_t, int, int, int, int, int>;
+    static std::map<Key, CUtensorMap> cache;
+    static std::mutex mu;
+    int device = 0;
+    cudaGetDevice(&device);
+    const Key key{base, dtype, rows, k, box_rows, device};
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        auto it = cache.find(key);
+        if (it != cache.end()) {
+            *tm = it->second;
+            return CUTE_B200_OK;
+        }
+    }
+    EncodeTiledFn encode;
+    CB_TRY(encode_fn(&encode));
+    const cuuint64_t dims[2] = {cuuint64_t(k), cuuint64_t(rows)};
+    const cuuint64_t strides[1] = {cuuint64_t(k) * 2};
+    const cuuint32_t box[2] = {cuuint32_t(BK), cuuint32_t(box_rows)};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = encode(tm, dtype == CUTE_B200_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                              2, reinterpret_cast<void *>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(CUTE_B200_ERR_CUDA, "cuTensorMapEncodeTiled failed: CUresult %d (rows %d, k %d, box %d)", int(r), rows, k,
+                    box_rows);
+    std::lock_guard<std::mutex> lock(mu);
+    if (cache.size() > 4096) cache.clear();
+    cache[key] = *tm;
+    return CUTE_B200_OK;
+}
+
+template <int CTA_GROUP, int BN, bool C_BF16>
+cute_b200_status launch(const CUtensorMap &tmA, const CUtensorMap &tmB, GemmParams p, int sm_count,
+                        cudaStream_t stream) {
+    using C = Cfg<CTA_GROUP, BN>;
+    p.m_tiles = (p.M + BM * CTA_GROUP - 1) / (BM * CTA_GROUP);
+    p.n_tiles = (p.N + BN - 1) / BN;
+    const long long tiles = (long long)p.m_tiles * p.n_tiles;
+    int clusters = sm_count / CTA_GROUP;
+    if (tiles < clusters) clusters = int(tiles);
+    // Walk about sqrt(#concurrent tiles) row tiles before moving to the next
+    // column so that a wave of CTAs covers a near-square patch of C.
+    int gm = 1;
+    while (gm * gm * 2 <= clusters) gm *= 2;
+    p.group_m = gm < p.m_tiles ? gm : p.m_tiles;
+    if (p.group_m < 1) p.group_m = 1;
+
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(unsigned(clusters * CTA_GROUP));
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = C::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CTA_GROUP;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    CB_CUDA(cudaLaunchKernelEx(&cfg, gemm_tn_kernel<CTA_GROUP, BN, C_BF16>, tmA, tmB, p));
+    count_launch();
+    return CUTE_B200_OK;
+}
+
+template <int CTA_GROUP, int BN, bool C_BF16>
+cute_b200_status set_smem_limit() {
+    CB_CUDA(cudaFuncSetAttribute(gemm_tn_kernel<CTA_GROUP, BN, C_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 Cfg<CTA_GROUP, BN>::SMEM_BYTES));
+    return CUTE_B200_OK;
+}
+
+}  // namespace
+
+cute_b200_status gemm_tn_init(const DeviceState &) {
+    CB_TRY((set_smem_limit<1, 128, false>()));
+    CB_TRY((set_smem_limit<1, 128, true>()));
+    CB_TRY((set_smem_limit<1, 256, false>()));
+    CB_TRY((set_smem_limit<1, 256, true>()));
+    CB_TRY((set_smem_limit<2, 128, false>()));
+    CB_TRY((set_smem_limit<2, 128, true>()));
+    CB_TRY((set_smem_limit<2, 256, false>()));
+    CB_TRY((set_smem_limit<2, 256, true>()));
+    return CUTE_B200_OK;
+}
+
+cute_b200_status gemm_tn(const cute_b200_gemm_desc &d, uint64_t a, uint64_t b, uint64_t c, cudaStream_t stream,
+                         const DeviceState &dev) {
+    if (d.m <= 0 || d.n <= 0 || d.k < 0)
+        return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "gemm_tn: invalid size %dx%dx%d", d.m, d.n, d.k);
+    if (d.ab_dtype != CUTE_B200_F16 && d.ab_dtype != CUTE_B200_BF16)
+        return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "gemm_tn takes f16 or bf16 inputs, not dtype %d", d.ab_dtype);
+    if (d.c_dtype != CUTE_B200_F32 && d.c_dtype != CUTE_B200_BF16)
+        return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "gemm_tn writes f32 or bf16, not dtype %d", d.c_dtype);
+    if (d.k % 8) return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "gemm_tn: k must be a multiple of 8, got %d", d.k);
+    if (d.tile_n != 0 && d.tile_n != 128 && d.tile_n != 256)
+        return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "gemm_tn: tile_n must be 0, 128 or 256, got %d", d.tile_n);
+    if (d.cta_group < 0 || d.cta_group > 2)
+        return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "gemm_tn: cta_group must be 0, 1 or 2, got %d", d.cta_group);
+    if (!c) return fail(CUTE_B200_ERR_NULL_POINTER, "gemm_tn: C is null");
+    const bool c_bf16 = d.c_dtype == CUTE_B200_BF16;
+    if (c & (c_bf16 ? 1u : 3u)) return fail(CUTE_B200_ERR_MISALIGNED, "gemm_tn: C is not aligned to its element size");
+
+    if (d.k == 0) {
+        const size_t count = size_t(d.m) * d.n;
+        const unsigned blocks = unsigned((count + 255) / 256);
+        if (c_bf16) gemm_k0_kernel<true><<<blocks, 256, 0, stream>>>(reinterpret_cast<void *>(c), count, d.alpha, d.beta);
+        else gemm_k0_kernel<false><<<blocks, 256, 0, stream>>>(reinterpret_cast<void *>(c), count, d.alpha, d.beta);
+        CB_CUDA(cudaGetLastError());
+        count_launch();
+        return CUTE_B200_OK;
+    }
+    if (!a || !b) return fail(CUTE_B200_ERR_NULL_POINTER, "gemm_tn: A or B is null");
+    if ((a | b) & 15u) return fail(CUTE_B200_ERR_MISALIGNED, "gemm_tn: A and B must be 16-byte aligned");
+
+    const int bn = d.tile_n ? d.tile_n : (d.n > 128 ? 256 : 128);
+    const int group = d.cta_group ? d.cta_group : (d.m > BM ? 2 : 1);
+
+    GemmParams p = {};
+    p.C = reinterpret_cast<void *>(c);
+    p.M = d.m;
+    p.N = d.n;
+    p.K = d.k;
+    p.ldc = d.n;
+    p.alpha = d.alpha;
+    p.beta = d.beta;
+    p.status = dev.status_word;
+    const size_t c_elem = c_bf16 ? 2 : 4;
+    p.c_vec_ok = ((c & 15u) == 0 && (size_t(d.n) * c_elem) % 16 == 0) ? 1 : 0;
+    const uint32_t fmt = d.ab_dtype == CUTE_B200_BF16 ? 1u : 0u;
+    // Instruction descriptor: f32 accumulator, A and B format, both K-major,
+    // N >> 3 at bit 17, M >> 4 at bit 24 (M counts the rows of the whole pair).
+    p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(bn >> 3) << 17) | (uint32_t((BM * group) >> 4) << 24);
+
+    CUtensorMap tmA, tmB;
+    CB_TRY(make_tensor_map(&tmA, a, d.ab_dtype, d.m, d.k, BM));
+    CB_TRY(make_tensor_map(&tmB, b, d.ab_dtype, d.n, d.k, bn / group));
+
+#define CB_GEMM_CASE(G, N_, BF)                                                       \
+    if (group == G && bn == N_ && c_bf16 == BF) return launch<G, N_, BF>(tmA, tmB, p, dev.sm_count, stream);
+    CB_GEMM_CASE(1, 128, false)
+    CB_GEMM_CASE(1, 128, true)
+    CB_GEMM_CASE(1, 256, false)
+    CB_GEMM_CASE(1, 256, true)
+    CB_GEMM_CASE(2, 128, false)
+    CB_GEMM_CASE(2, 128, true)
+    CB_GEMM_CASE(2, 256, false)
+    CB_GEMM_CASE(2, 256, true)
+#undef CB_GEMM_CASE
+    return fail(CUTE_B200_ERR_UNSUPPORTED, "gemm_tn: no kernel for cta_group %d, tile_n %d", group, bn);
+}
+
+}  // namespace cb

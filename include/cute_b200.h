@@ -1,0 +1,184 @@
+/*
+ * cute_b200.h - C ABI of libcute_b200.so
+ *
+ * A B200 (sm_100a) implementation of the kernels the cute-rs crate exists to
+ * run: the tensor-core GEMMs `tensorop_gemm` / `runtime_gemm`, the SIMT
+ * `sgemm_nt`, and `elementwise_add`.  The library sits beside the crate's
+ * CUDA launcher (src/cuda.rs) and takes over the launch of those kernels;
+ * everything else keeps going through the crate's own PTX path.
+ *
+ * Conventions (those of src/cuda.rs, so a Rust shim can bind this 1:1):
+ *   - device pointers travel as uint64_t, like `CuDevicePtr` (src/cuda.rs:35);
+ *   - the caller owns every buffer; the library owns only cached TMA
+ *     descriptors, a small per-device status word and optional workspaces;
+ *   - every entry point returns a status code and never throws or aborts;
+ *     `cute_b200_last_error()` gives the message a `CudaError` would carry
+ *     (src/cuda.rs:71-86, 532-546);
+ *   - launches are asynchronous on `stream` (a CUstream/cudaStream_t; NULL is
+ *     the legacy default stream the reference launches on, src/cuda.rs:382);
+ *   - one host thread per device at a time, no internal locking beyond the
+ *     descriptor cache (the reference's types are !Send + !Sync).
+ *
+ * There is no CPU fallback: without a CUDA device every compute entry point
+ * returns CUTE_B200_ERR_NO_DEVICE.
+ */
+#ifndef CUTE_B200_H
+#define CUTE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#if defined(__GNUC__)
+#pragma GCC visibility push(default)
+#endif
+
+typedef int32_t cute_b200_status;
+
+enum {
+    CUTE_B200_OK = 0,
+    CUTE_B200_ERR_INVALID_ARGUMENT = -1, /* a size, count, dtype or launch shape the kernel cannot take */
+    CUTE_B200_ERR_MISALIGNED = -2,       /* a pointer or pitch breaks the 16-byte rule of param_tensor / TMA */
+    CUTE_B200_ERR_UNSUPPORTED = -3,      /* a kernel name or option this library does not implement */
+    CUTE_B200_ERR_NO_DEVICE = -4,        /* no usable sm_100 device */
+    CUTE_B200_ERR_DEVICE_TIMEOUT = -5,   /* a bounded wait inside a kernel gave up; see cute_b200_device_status */
+    CUTE_B200_ERR_CUDA = -6,             /* a CUDA runtime/driver call failed; message in cute_b200_last_error */
+    CUTE_B200_ERR_NULL_POINTER = -7
+};
+
+typedef enum { CUTE_B200_F16 = 0, CUTE_B200_BF16 = 1, CUTE_B200_F32 = 2, CUTE_B200_I32 = 3 } cute_b200_dtype;
+
+/* Static name of a status code.  Counterpart of cuGetErrorName as used by
+ * check() in src/cuda.rs:532-546. */
+const char *cute_b200_status_string(cute_b200_status status);
+
+/* Message of the calling thread's most recent failure ("" if none), worded
+ * like the reference's errors ("argument 3 (`n`) must be a multiple of 128,
+ * got 100", src/sim/mod.rs:328-385; "<call> failed: <name>", src/cuda.rs:540). */
+const char *cute_b200_last_error(void);
+
+/* Make `device_ordinal` usable by this library on the calling thread: selects
+ * the device (its primary context, which CudaContext::new retains too,
+ * src/cuda.rs:210-224), checks that it is sm_100, raises the kernels'
+ * dynamic shared-memory limit and allocates the status word.  Idempotent.
+ * Other entry points call it lazily for the current device. */
+cute_b200_status cute_b200_init(int32_t device_ordinal);
+
+/* ---- tensor-core GEMM ------------------------------------------------------
+ * C = alpha * (A * B^T) + beta * C
+ *   A: (m, k) row-major, k contiguous ("K-major"), f16 or bf16
+ *   B: (n, k) row-major, k contiguous, same type as A
+ *   C: (m, n) row-major, f32 or bf16
+ * f32 accumulation on the tcgen05 tensor cores.  With alpha == 1 and
+ * beta == 0 C is write-only, as in tensorop_gemm (examples/tensorop_gemm.rs:
+ * 161-162); otherwise the epilogue is the three-rounding form of sgemm
+ * (examples/sgemm.rs:75-79).  Replaces the kernels built by
+ * tensorop_gemm::build_typed (examples/tensorop_gemm.rs:51-164) and
+ * runtime_gemm::build (examples/runtime_gemm.rs:22-105).
+ *
+ * m, n >= 1; k >= 0 (k == 0 stores the beta term only); k must be a multiple
+ * of 8 and A, B 16-byte aligned (TMA row pitch); C aligned to 16 bytes.
+ * The reference's own limits (multiples of 128 / 128 / 32) are enforced by
+ * cute_b200_launch, which mirrors its launch checks. */
+typedef struct {
+    int32_t m, n, k;
+    int32_t ab_dtype; /* CUTE_B200_F16 or CUTE_B200_BF16 */
+    int32_t c_dtype;  /* CUTE_B200_F32 or CUTE_B200_BF16 */
+    float alpha, beta;
+    int32_t tile_n;    /* 0 = choose; 128 or 256 */
+    int32_t cta_group; /* 0 = choose; 1 = one CTA per tile; 2 = CTA pair per 256-row tile */
+    int32_t reserved[4]; /* zero */
+} cute_b200_gemm_desc;
+
+cute_b200_status cute_b200_gemm_tn(const cute_b200_gemm_desc *desc, uint64_t dA, uint64_t dB, uint64_t dC,
+                                   void *stream);
+
+/* ---- SIMT sgemm ------------------------------------------------------------
+ * C = alpha * (A * B^T) + beta * C, all f32 and column-major: a[i + l*m],
+ * b[j + l*n], c[i + j*m].  fma.rn.f32 accumulation with l ascending and a
+ * mul, mul, add epilogue, so the result is bit-identical to the reference
+ * kernel's (examples/sgemm.rs:23-81).  m and n multiples of 128, k >= 0. */
+cute_b200_status cute_b200_sgemm_nt(int32_t m, int32_t n, int32_t k, float alpha, float beta, uint64_t dA,
+                                    uint64_t dB, uint64_t dC, void *stream);
+
+/* ---- elementwise add -------------------------------------------------------
+ * out[i] = x[i] + y[i] for i < n, IEEE binary32, no flush to zero; elements
+ * at and past n are not touched.  Replaces elementwise_add::{naive, tiled}
+ * (examples/elementwise_add.rs:23-80).  Pointers need 4-byte alignment; the
+ * 128-bit path runs when all three share their offset within 16 bytes. */
+cute_b200_status cute_b200_elementwise_add_f32(uint64_t dX, uint64_t dY, uint64_t dOut, uint64_t n, void *stream);
+
+/* ---- launch by kernel name -------------------------------------------------
+ * Counterpart of CudaContext::launch_on_device (src/cuda.rs:414-426): the
+ * arguments in declaration order, one slot each, plus the launch shape.  The
+ * checks of check_launch (src/sim/mod.rs:328-385) are applied with the same
+ * messages: argument count, block size, grid/cluster divisibility, the block
+ * size the kernel was built for, buffer dtype and length, scalar multiples.
+ * Problem sizes follow from the grid and the buffer lengths exactly as the
+ * reference kernels derive them.  Known names: tensorop_gemm,
+ * tensorop_gemm_unswizzled, tensorop_gemm_bf16, tensorop_gemm_bf16_unswizzled
+ * (a, b, c), runtime_gemm (a, b, c, n, k), sgemm_nt (a, b, c, alpha, beta),
+ * elementwise_add_naive, elementwise_add_tiled (a, b, c). */
+typedef struct {
+    int32_t is_scalar; /* 0 = buffer, 1 = scalar */
+    int32_t dtype;     /* cute_b200_dtype of the elements / the scalar */
+    uint64_t value;    /* device pointer, or the scalar's bits in the low bytes (src/cuda.rs:332-349) */
+    uint64_t len;      /* buffers: number of elements */
+} cute_b200_arg;
+
+typedef struct {
+    uint32_t grid[3], block[3], cluster[3]; /* LaunchConfig, src/sim/mod.rs:41-61 */
+} cute_b200_launch_config;
+
+cute_b200_status cute_b200_launch(const char *kernel_name, const cute_b200_launch_config *cfg,
+                                  const cute_b200_arg *args, int32_t num_args, void *stream);
+
+/* Counterpart of CudaContext::launch (src/cuda.rs:443-473): buffer arguments
+ * hold HOST pointers; every buffer is uploaded, the kernel runs, the call
+ * waits for it, and every buffer is copied back in place.  `seconds`, if not
+ * NULL, receives the kernel's device time (LaunchStats.kernel_seconds,
+ * src/cuda.rs:65-69), measured with CUDA events. */
+cute_b200_status cute_b200_launch_host(const char *kernel_name, const cute_b200_launch_config *cfg,
+                                       const cute_b200_arg *args, int32_t num_args, double *seconds);
+
+/* ---- device buffers (CudaContext::upload / download / DeviceBuffer drop,
+ * src/cuda.rs:282-304, 491-502) ------------------------------------------- */
+cute_b200_status cute_b200_upload(const void *host, uint64_t bytes, uint64_t *device_out);
+cute_b200_status cute_b200_download(uint64_t device, void *host, uint64_t bytes);
+cute_b200_status cute_b200_free(uint64_t device);
+/* CudaContext::synchronize (src/cuda.rs:306-311); also folds a kernel's
+ * bounded-wait report into the return value. */
+cute_b200_status cute_b200_synchronize(void);
+
+/* ---- row-sharded GEMM for several GPUs ------------------------------------
+ * One process (or thread) per GPU.  Rank r of `world` owns the contiguous
+ * row block [row_begin, row_begin + rows) of A and C; B is whole in every
+ * GPU's own memory.  No data crosses between GPUs here: a caller that wants
+ * C replicated all-gathers the row blocks afterwards (NCCL).  The reference
+ * has no multi-GPU path; this extends its launcher. */
+cute_b200_status cute_b200_shard_rows(int32_t m, int32_t world, int32_t rank, int32_t *row_begin, int32_t *rows);
+/* desc->m is the GLOBAL row count; dA_shard points at this rank's rows of A,
+ * dC_base at row 0 of a full-size C (c_is_full != 0) or at this rank's block. */
+cute_b200_status cute_b200_gemm_tn_shard(const cute_b200_gemm_desc *desc, int32_t world, int32_t rank,
+                                         uint64_t dA_shard, uint64_t dB, uint64_t dC_base, int32_t c_is_full,
+                                         void *stream);
+
+/* ---- bounded waits ----------------------------------------------------------
+ * Every spin on an mbarrier inside the GEMM kernel has a time limit.  A CTA
+ * that gives up records {code, role/stage, block index, parity} here and the
+ * kernel drains and returns instead of hanging.  Reads and clears the word
+ * of the current device (synchronises the device).  out[0] == 0: no report. */
+cute_b200_status cute_b200_device_status(uint32_t out[4]);
+
+/* Number of kernels this library has launched from the calling process. */
+uint64_t cute_b200_launch_count(void);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+#ifdef __cplusplus
+}
+#endif
+#endif /* CUTE_B200_H */
