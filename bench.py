@@ -1,0 +1,355 @@
+#!/usr/bin/env python
+"""Benchmark of the cute-rs hot path on B200: bf16 GEMM TFLOP/s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+N = 1  : runtime_gemm, bf16 in / bf16 out, 8192 x 8192 x 8192, normal(0, 0.02)
+         inputs, alpha 1, beta 0 - one step is one GEMM launch.
+N > 1  : (launched by torchrun, one rank per GPU) the row-sharded GEMM
+         32768 x 32768 x 8192: rank r computes its contiguous block of rows of
+         C from its rows of A and a full copy of B in its own memory; no
+         collective on the data path (the optional all-gather of C is timed
+         separately and reported under "replicated").
+
+`value` is the whole-job TFLOP/s with operands resident in HBM, timed with
+CUDA events on the launching stream (max over ranks).  `e2e` is the same
+metric through the host-buffer C-ABI call with the host<->device copies inside
+the timed region.  `roofline` compares the dominant kernel with the measured
+cuBLAS bf16 peak of this pool; `cpu_baseline` times the CPU oracle on the host
+cores.  `--impl reference` times the reference's CPU arithmetic (the oracle:
+the reference itself is Rust and cannot be built in this image) on a bounded
+sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "bf16_gemm_tflops"
+UNIT = "TFLOP/s"
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+# DRAM bytes (read + write) of one 8192^3 bf16->bf16 launch of gemm_tn_kernel from the
+# ncu capture summarised in profiles/gemm_tn_8192_bf16_ncu.md; None until captured.
+NCU_TRAFFIC_8192 = None
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        p["_source"] = "measured"
+        return p
+    p = dict(FALLBACK_PEAKS)
+    p["_source"] = "fallback"
+    return p
+
+
+def workload(n_gpus: int):
+    if n_gpus == 1:
+        return dict(name="runtime_gemm bf16 8192x8192x8192 (normal(0,0.02) seed 3, alpha=1, beta=0, bf16 C)",
+                    m=8192, n=8192, k=8192, seed=3)
+    return dict(name="row-sharded bf16 GEMM 32768x32768x8192 (normal(0,0.02) seed 4, bf16 C, B replicated)",
+                m=32768, n=32768, k=8192, seed=4)
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while a region runs."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {"hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+                 "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+                 "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+                 "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4),
+                 "hw_power_brake": getattr(nv, "nvmlClocksEventReasonHwPowerBrakeSlowdown", 0x80)}
+        get = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or nv.nvmlDeviceGetCurrentClocksThrottleReasons
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                mask = get(self.h)
+                for k, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread:
+            self._thread.join()
+
+    def summary(self):
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "samples": len(self.samples), "reasons": sorted(self.reasons)}
+
+
+def run_reference(args):
+    """The reference's CPU path (restated: the oracle) on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import numpy as np
+    import oracle
+    w = workload(args.gpus)
+    rows = 1024 if args.gpus == 1 else 256  # bounded sample: a band of rows of the same GEMM
+    rng = np.random.default_rng(w["seed"])
+    a = oracle.f32_to_bf16_bits(rng.normal(0, 0.02, (rows, w["k"])).astype(np.float32))
+    b = oracle.f32_to_bf16_bits(rng.normal(0, 0.02, (w["n"], w["k"])).astype(np.float32))
+    flop = 2.0 * rows * w["n"] * w["k"]
+    for _ in range(min(args.warmup, 2)):
+        oracle.gemm_tn(a, b, oracle.BF16, oracle.BF16)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        oracle.gemm_tn(a, b, oracle.BF16, oracle.BF16)
+    dt = (time.perf_counter() - t0) / args.steps
+    value = flop / dt / 1e12
+    sample = f"{rows} of {w['m']} rows of C per step (full n, k); the oracle's blocked sequential-k f32 GEMM incl. its bf16->f32 packing"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak" if args.gpus == 1 else "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": w["name"]},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "reference = C restatement of Kernel::simulate's arithmetic (oracle/); the Rust crate cannot be built here",
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--skip-extras", action="store_true", help="skip cpu_baseline / e2e / secondary kernels (profiling runs)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    import torch.distributed as dist
+    from cute_rs_b200 import _lib as lib
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {args.gpus}")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    lib.init(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    w = workload(world)
+    M, N, K = w["m"], w["n"], w["k"]
+    row_begin, rows = lib.shard_rows(M, world, rank)
+    g = torch.Generator(device="cuda").manual_seed(w["seed"])
+    B = (torch.randn(N, K, device="cuda", generator=g) * 0.02).bfloat16()  # same on every rank
+    ga = torch.Generator(device="cuda").manual_seed(w["seed"] * 1000 + rank)
+    A = (torch.randn(rows, K, device="cuda", generator=ga) * 0.02).bfloat16()
+    C = torch.empty(rows, N, device="cuda", dtype=torch.bfloat16)
+    desc = lib.gemm_desc(M, N, K, lib.BF16, lib.BF16)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def step():
+        lib.gemm_tn_shard(desc, world, rank, A.data_ptr(), B.data_ptr(), C.data_ptr(), False, stream)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = lib.launch_count()
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        barrier()
+    launches = lib.launch_count() - launches0
+    ms_total = e0.elapsed_time(e1)
+    status = lib.device_status()
+    if status[0] != 0:
+        raise SystemExit(f"kernel reported a bounded-wait timeout: {status}")
+    t = torch.tensor([ms_total], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t.item()) / args.steps
+    flop = 2.0 * M * N * K
+    value = flop / (ms_step * 1e-3) / 1e12
+
+    pk = peaks()
+    region_s = ms_step * args.steps * 1e-3
+    peak_kind = "bf16_tflops" if region_s < 1.0 else "bf16_tflops_sustained"
+    per_gpu_tflops = value / world
+    roofline = {"bound": "tensor", "achieved": per_gpu_tflops, "peak": pk[peak_kind], "unit": "TFLOP/s",
+                "frac": per_gpu_tflops / pk[peak_kind], "traffic": NCU_TRAFFIC_8192 if world == 1 else None,
+                "kernel": "gemm_tn_kernel<cta_group 2, tile 256x256x64>", "peak_kind": f"{peak_kind} ({pk['_source']})",
+                "frac_of_nominal_2250": per_gpu_tflops / 2250.0,
+                "algorithmic_flop_per_launch": 2.0 * rows * N * K}
+
+    out = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+           "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak" if world == 1 else "strong",
+           "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+           "config": {"workload": w["name"], "rows_per_gpu": rows, "l2": "operands (A+B+C >= 384 MB per GPU) exceed the 126 MB L2",
+                      "timing": "cuda events on the launching stream, max over ranks"},
+           "roofline": roofline, "clocks": clocks.summary(), "gpu_launches": int(launches)}
+
+    # ---- end to end through the host-buffer C-ABI call --------------------------------
+    if not args.skip_extras:
+        hA = torch.empty(rows, K, dtype=torch.bfloat16).pin_memory()
+        hB = torch.empty(N, K, dtype=torch.bfloat16).pin_memory()
+        hC = torch.empty(rows, N, dtype=torch.bfloat16).pin_memory()
+        hA.copy_(A)
+        hB.copy_(B)
+        sub = lib.gemm_desc(rows, N, K, lib.BF16, lib.BF16)
+        e2e_steps = max(3, min(args.steps, 10))
+        for _ in range(2):
+            lib.gemm_tn_host(sub, hA.data_ptr(), hB.data_ptr(), hC.data_ptr())
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            lib.gemm_tn_host(sub, hA.data_ptr(), hB.data_ptr(), hC.data_ptr())  # synchronous: returns with C on the host
+        checksum = float(hC[0, 0])  # the step's result is read on the host
+        dt = time.perf_counter() - t0
+        tt = torch.tensor([dt], device="cuda", dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        dt = float(tt.item()) / e2e_steps
+        out["e2e"] = {"value": flop / dt / 1e12, "unit": UNIT, "h2d_bytes_per_step": (rows * K + N * K) * 2,
+                      "d2h_bytes_per_step": rows * N * 2, "ms_per_step": dt * 1e3, "steps": e2e_steps,
+                      "api": "cute_b200_gemm_tn_host (pinned host buffers, synchronous)", "checksum": checksum}
+        lib.release_workspace()
+        del hA, hB, hC
+
+    # ---- optional replicated C (all-gather over NVLink), N > 1 only ----------------------
+    if world > 1 and not args.skip_extras:
+        full = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        for _ in range(2):
+            step()
+            dist.all_gather_into_tensor(full, C)
+        barrier()
+        e0.record()
+        reps = max(3, min(args.steps, 10))
+        for _ in range(reps):
+            step()
+            dist.all_gather_into_tensor(full, C)
+        e1.record()
+        barrier()
+        tt = torch.tensor([e0.elapsed_time(e1) / reps], device="cuda", dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        out["replicated"] = {"value": flop / (float(tt.item()) * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": float(tt.item()),
+                             "collective": "ncclAllGather of the bf16 row blocks of C after the GEMM"}
+        del full
+
+    # ---- secondary kernels and the CPU baseline: rank 0 of a 1-GPU run only ----------------
+    if world == 1 and not args.skip_extras:
+        out["elementwise_add"] = bench_add(lib, torch, pk)
+        out["sgemm"] = bench_sgemm(lib, torch)
+        out["cpu_baseline"] = cpu_baseline(A, B, M, N, K)
+
+    if rank == 0:
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def bench_add(lib, torch, pk):
+    n = 1 << 28
+    g = torch.Generator(device="cuda").manual_seed(1)
+    x = torch.rand(n, device="cuda", generator=g) * 2 - 1
+    y = torch.rand(n, device="cuda", generator=g) * 2 - 1
+    o = torch.empty(n, device="cuda")
+    s = torch.cuda.current_stream().cuda_stream
+    for _ in range(3):
+        lib.elementwise_add_f32(x.data_ptr(), y.data_ptr(), o.data_ptr(), n, s)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(20):
+        lib.elementwise_add_f32(x.data_ptr(), y.data_ptr(), o.data_ptr(), n, s)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / 20
+    gbs = 12.0 * n / ms / 1e6
+    return {"workload": "elementwise_add f32 2^28 elements, uniform[-1,1) seed 1 (3 x 1 GiB, larger than L2)",
+            "gbs": gbs, "ms": ms, "bound": "hbm", "peak": pk["hbm_gbs"], "frac": gbs / pk["hbm_gbs"],
+            "peak_kind": f"hbm_gbs ({pk['_source']})", "frac_of_nominal_8000": gbs / 8000.0,
+            "algorithmic_bytes_per_launch": 12 * n}
+
+
+def bench_sgemm(lib, torch):
+    n = 4096
+    g = torch.Generator(device="cuda").manual_seed(2)
+    a, b, c = (torch.rand(n * n, device="cuda", generator=g) * 2 - 1 for _ in range(3))
+    s = torch.cuda.current_stream().cuda_stream
+    for _ in range(3):
+        lib.sgemm_nt(n, n, n, 1.5, 0.5, a.data_ptr(), b.data_ptr(), c.data_ptr(), s)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(10):
+        lib.sgemm_nt(n, n, n, 1.5, 0.5, a.data_ptr(), b.data_ptr(), c.data_ptr(), s)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / 10
+    return {"workload": "sgemm_nt f32 4096^3 column-major, alpha 1.5, beta 0.5", "tflops": 2.0 * n ** 3 / ms / 1e9, "ms": ms,
+            "bound": "fp32 FFMA pipe", "peak_nominal": 148 * 128 * 2 * 1.965e9 / 1e12}
+
+
+def cpu_baseline(A, B, M, N, K):
+    """The oracle timed on the host cores: one pass over a band of rows of the
+    same GEMM (test infrastructure used as the reported CPU baseline only)."""
+    import numpy as np
+    import torch
+    import oracle
+    rows = 2048
+    a = A[:rows].view(torch.int16).cpu().numpy().view(np.uint16)
+    b = B.view(torch.int16).cpu().numpy().view(np.uint16)
+    oracle.gemm_tn(a[:64], b, oracle.BF16, oracle.BF16)  # build + page in
+    t0 = time.perf_counter()
+    oracle.gemm_tn(a, b, oracle.BF16, oracle.BF16)
+    dt = time.perf_counter() - t0
+    return {"value": 2.0 * rows * N * K / dt / 1e12, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port",
+            "sample": f"rows [0, {rows}) of the {M}x{N}x{K} GEMM, one pass, {dt:.2f} s"}
+
+
+if __name__ == "__main__":
+    main()

@@ -25,6 +25,7 @@ F16, BF16, F32, I32 = 0, 1, 2, 3
 
 EXPORTS = (
     "cute_b200_status_string", "cute_b200_last_error", "cute_b200_init", "cute_b200_gemm_tn", "cute_b200_sgemm_nt",
+    "cute_b200_gemm_tn_host", "cute_b200_release_workspace",
     "cute_b200_elementwise_add_f32", "cute_b200_launch", "cute_b200_launch_host", "cute_b200_upload",
     "cute_b200_download", "cute_b200_free", "cute_b200_synchronize", "cute_b200_shard_rows",
     "cute_b200_gemm_tn_shard", "cute_b200_device_status", "cute_b200_launch_count",
@@ -73,6 +74,8 @@ def load() -> ctypes.CDLL:
     L.cute_b200_last_error.restype = cp
     L.cute_b200_init.argtypes = [i32]
     L.cute_b200_gemm_tn.argtypes = [ctypes.POINTER(GemmDesc), u64, u64, u64, vp]
+    L.cute_b200_gemm_tn_host.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, vp, ctypes.POINTER(ctypes.c_double)]
+    L.cute_b200_release_workspace.argtypes = []
     L.cute_b200_sgemm_nt.argtypes = [i32, i32, i32, f32, f32, u64, u64, u64, vp]
     L.cute_b200_elementwise_add_f32.argtypes = [u64, u64, u64, u64, vp]
     L.cute_b200_launch.argtypes = [cp, ctypes.POINTER(LaunchCfg), ctypes.POINTER(Arg), i32, vp]
@@ -117,6 +120,17 @@ def gemm_desc(m, n, k, ab_dtype, c_dtype, alpha=1.0, beta=0.0, tile_n=0, cta_gro
 
 def gemm_tn(desc: GemmDesc, dA: int, dB: int, dC: int, stream: int = 0) -> None:
     check(load().cute_b200_gemm_tn(ctypes.byref(desc), dA, dB, dC, stream))
+
+
+def gemm_tn_host(desc: GemmDesc, hA: int, hB: int, hC: int) -> float:
+    """GEMM on host buffers (addresses); returns the kernel's device seconds."""
+    sec = ctypes.c_double(0.0)
+    check(load().cute_b200_gemm_tn_host(ctypes.byref(desc), hA, hB, hC, ctypes.byref(sec)))
+    return sec.value
+
+
+def release_workspace() -> None:
+    check(load().cute_b200_release_workspace())
 
 
 def gemm_tn_shard(desc: GemmDesc, world: int, rank: int, dA_shard: int, dB: int, dC_base: int, c_is_full: bool,

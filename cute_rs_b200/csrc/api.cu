@@ -347,6 +347,85 @@ cute_b200_status cute_b200_gemm_tn(const cute_b200_gemm_desc *desc, uint64_t dA,
     return gemm_tn(*desc, dA, dB, dC, static_cast<cudaStream_t>(stream), *dev);
 }
 
+// Grow-only device staging buffers of the host-buffer entry points, per device.
+struct Workspace {
+    void *ptr[3] = {nullptr, nullptr, nullptr};
+    size_t bytes[3] = {0, 0, 0};
+};
+static Workspace g_workspace[kMaxDevices];
+
+static cute_b200_status workspace_get(int device, int slot, size_t bytes, void **out) {
+    Workspace &w = g_workspace[device];
+    if (w.bytes[slot] < bytes) {
+        if (w.ptr[slot]) cudaFree(w.ptr[slot]);
+        w.ptr[slot] = nullptr;
+        w.bytes[slot] = 0;
+        CB_CUDA(cudaMalloc(&w.ptr[slot], bytes));
+        w.bytes[slot] = bytes;
+    }
+    *out = w.ptr[slot];
+    return CUTE_B200_OK;
+}
+
+cute_b200_status cute_b200_release_workspace(void) {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) {
+        cudaGetLastError();
+        return CUTE_B200_OK;
+    }
+    Workspace &w = g_workspace[device];
+    for (int i = 0; i < 3; i++) {
+        if (w.ptr[i]) cudaFree(w.ptr[i]);
+        w.ptr[i] = nullptr;
+        w.bytes[i] = 0;
+    }
+    return CUTE_B200_OK;
+}
+
+cute_b200_status cute_b200_gemm_tn_host(const cute_b200_gemm_desc *desc, const void *hA, const void *hB, void *hC,
+                                        double *seconds) {
+    if (!desc) return fail(CUTE_B200_ERR_NULL_POINTER, "gemm_tn_host: desc is null");
+    if (desc->m <= 0 || desc->n <= 0 || desc->k < 0)
+        return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "gemm_tn: invalid size %dx%dx%d", desc->m, desc->n, desc->k);
+    if (!hC || (desc->k > 0 && (!hA || !hB))) return fail(CUTE_B200_ERR_NULL_POINTER, "gemm_tn_host: null buffer");
+    DeviceState *dev;
+    CB_TRY(current_device(&dev));
+    int device = 0;
+    CB_CUDA(cudaGetDevice(&device));
+    const size_t a_bytes = size_t(desc->m) * desc->k * 2, b_bytes = size_t(desc->n) * desc->k * 2;
+    const size_t c_bytes = size_t(desc->m) * desc->n * (desc->c_dtype == CUTE_B200_BF16 ? 2 : 4);
+    void *dA, *dB, *dC;
+    CB_TRY(workspace_get(device, 0, a_bytes ? a_bytes : 16, &dA));
+    CB_TRY(workspace_get(device, 1, b_bytes ? b_bytes : 16, &dB));
+    CB_TRY(workspace_get(device, 2, c_bytes, &dC));
+    cudaStream_t stream = nullptr;
+    if (a_bytes) CB_CUDA(cudaMemcpyAsync(dA, hA, a_bytes, cudaMemcpyHostToDevice, stream));
+    if (b_bytes) CB_CUDA(cudaMemcpyAsync(dB, hB, b_bytes, cudaMemcpyHostToDevice, stream));
+    const bool reads_c = !(desc->alpha == 1.0f && desc->beta == 0.0f);
+    if (reads_c) CB_CUDA(cudaMemcpyAsync(dC, hC, c_bytes, cudaMemcpyHostToDevice, stream));
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    if (seconds) {
+        CB_CUDA(cudaEventCreate(&e0));
+        CB_CUDA(cudaEventCreate(&e1));
+        cudaEventRecord(e0, stream);
+    }
+    cute_b200_status st = gemm_tn(*desc, reinterpret_cast<uint64_t>(dA), reinterpret_cast<uint64_t>(dB),
+                                  reinterpret_cast<uint64_t>(dC), stream, *dev);
+    if (seconds) cudaEventRecord(e1, stream);
+    if (st == CUTE_B200_OK) {
+        cudaError_t err = cudaMemcpyAsync(hC, dC, c_bytes, cudaMemcpyDeviceToHost, stream);
+        if (err != cudaSuccess) st = cuda_fail(err, "cudaMemcpyAsync");
+    }
+    if (st == CUTE_B200_OK) st = sync_and_check();
+    if (seconds) {
+        float ms = 0.0f;
+        if (st == CUTE_B200_OK && cudaEventElapsedTime(&ms, e0, e1) == cudaSuccess) *seconds = double(ms) * 1e-3;
+        cudaEventDestroy(e0);
+        cudaEventDestroy(e1);
+    }
+    return st;
+}
+
 cute_b200_status cute_b200_sgemm_nt(int32_t m, int32_t n, int32_t k, float alpha, float beta, uint64_t dA, uint64_t dB,
                                     uint64_t dC, void *stream) {
     DeviceState *dev;

@@ -95,6 +95,17 @@ typedef struct {
 cute_b200_status cute_b200_gemm_tn(const cute_b200_gemm_desc *desc, uint64_t dA, uint64_t dB, uint64_t dC,
                                    void *stream);
 
+/* The same GEMM on HOST buffers, the convention of CudaContext::launch
+ * (src/cuda.rs:443-473): A and B are uploaded, the kernel runs, the call waits
+ * and C is copied back (C is uploaded first only when beta != 0).  Device
+ * staging memory is kept by the library between calls and grows on demand;
+ * cute_b200_release_workspace frees it.  Pinned host memory makes the copies
+ * faster but is not required.  `seconds`, if not NULL, receives the kernel's
+ * device time. */
+cute_b200_status cute_b200_gemm_tn_host(const cute_b200_gemm_desc *desc, const void *hA, const void *hB, void *hC,
+                                        double *seconds);
+cute_b200_status cute_b200_release_workspace(void);
+
 /* ---- SIMT sgemm ------------------------------------------------------------
  * C = alpha * (A * B^T) + beta * C, all f32 and column-major: a[i + l*m],
  * b[j + l*n], c[i + j*m].  fma.rn.f32 accumulation with l ascending and a

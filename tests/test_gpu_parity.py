@@ -1,0 +1,392 @@
+"""Parity of the CUDA kernels with the CPU oracle, through the C ABI.
+
+Criteria are the reference's own (tests/gpu.rs): elementwise_add and sgemm
+bit-exact on any data; tensor-core GEMMs bit-exact on small-integer data and
+within 2*k*2^-23*sum|a*b| per element on data that has to round (plus one bf16
+unit in the last place when C is bf16).
+"""
+import numpy as np
+import pytest
+
+import oracle
+from tests.util import bf16_ulp, lcg_buffers, tensor_core_bound
+
+pytestmark = pytest.mark.gpu
+
+
+def dev(arr):
+    import torch
+    t = torch.from_numpy(np.ascontiguousarray(arr).view(np.int16) if arr.dtype == np.uint16 else np.ascontiguousarray(arr))
+    return t.cuda()
+
+
+def host(t, dtype):
+    a = t.cpu().numpy()
+    return a.view(np.uint16) if dtype == np.uint16 else a
+
+
+def run_gemm(lib, a_bits, b_bits, ab, cdt, alpha=1.0, beta=0.0, c0=None, tile_n=0, cta_group=0):
+    import torch
+    (m, k), n = a_bits.shape, b_bits.shape[0]
+    if c0 is None:
+        c0 = np.zeros((m, n), np.float32 if cdt == lib.F32 else np.uint16)
+    dA, dB, dC = dev(a_bits), dev(b_bits), dev(c0)
+    a_ptr = dA.data_ptr() if k else 0
+    b_ptr = dB.data_ptr() if k else 0
+    lib.gemm_tn(lib.gemm_desc(m, n, k, ab, cdt, alpha, beta, tile_n, cta_group), a_ptr, b_ptr, dC.data_ptr(), 0)
+    torch.cuda.synchronize()
+    assert lib.device_status() == (0, 0, 0, 0)
+    return host(dC, c0.dtype).reshape(m, n)
+
+
+def conv(lib, ab):
+    return oracle.f32_to_bf16_bits if ab == lib.BF16 else oracle.f32_to_f16_bits
+
+
+# ------------------------------------------------------------------ elementwise
+@pytest.mark.parametrize("n,offset", [(0, 0), (1, 0), (3, 1), (4095, 0), (4096, 0), (4097, 0), (4096, 1), (4096, 3),
+                                      (300 * 512, 0), (1 << 22, 2), ((1 << 22) + 5, 0)])
+def test_elementwise_add_bit_exact_with_ragged_ends(lib, gpu, n, offset):
+    import torch
+    rng = np.random.default_rng(n + offset)
+    x = rng.uniform(-1, 1, n + 8).astype(np.float32)
+    y = rng.uniform(-1, 1, n + 8).astype(np.float32)
+    if n > 16:
+        x[offset + 3], y[offset + 3] = np.float32(1e-45), np.float32(2e-45)  # subnormals must survive
+        x[offset + 5], y[offset + 5] = np.float32(np.inf), np.float32(-np.inf)
+    dx, dy = dev(x), dev(y)
+    out = torch.full((n + 8,), 7.0, device="cuda")
+    lib.elementwise_add_f32(dx.data_ptr() + 4 * offset, dy.data_ptr() + 4 * offset, out.data_ptr() + 4 * offset, n, 0)
+    torch.cuda.synchronize()
+    want = np.full(n + 8, 7.0, np.float32)
+    want[offset:offset + n] = oracle.elementwise_add(x[offset:offset + n], y[offset:offset + n])
+    assert np.array_equal(out.cpu().numpy().view(np.uint32), want.view(np.uint32))
+
+
+def test_elementwise_add_mixed_alignment_uses_scalar_kernel(lib, gpu):
+    import torch
+    n = 10007
+    rng = np.random.default_rng(3)
+    x, y = rng.uniform(-1, 1, n + 4).astype(np.float32), rng.uniform(-1, 1, n + 4).astype(np.float32)
+    dx, dy, out = dev(x), dev(y), torch.zeros(n + 4, device="cuda")
+    lib.elementwise_add_f32(dx.data_ptr() + 4, dy.data_ptr() + 8, out.data_ptr(), n, 0)
+    torch.cuda.synchronize()
+    assert np.array_equal(out.cpu().numpy()[:n], oracle.elementwise_add(x[1:n + 1], y[2:n + 2]))
+    assert not out.cpu().numpy()[n:].any()
+    with pytest.raises(lib.CuteB200Error) as e:
+        lib.elementwise_add_f32(dx.data_ptr() + 2, dy.data_ptr(), out.data_ptr(), 4, 0)
+    assert e.value.status == lib.ERR_MISALIGNED
+
+
+def test_elementwise_add_golden_and_lcg(lib, gpu, golden):
+    import torch
+    for small in (True, False):
+        a, b, _ = lcg_buffers([300 * 512, 300 * 512, 0], small=small)
+        da, db, out = dev(a), dev(b), torch.empty(300 * 512, device="cuda")
+        lib.elementwise_add_f32(da.data_ptr(), db.data_ptr(), out.data_ptr(), a.size, 0)
+        torch.cuda.synchronize()
+        got = out.cpu().numpy()
+        assert np.array_equal(got.view(np.uint32), oracle.elementwise_add(a, b).view(np.uint32))
+        if not small:
+            assert np.array_equal(got[golden["add_lcg_index"]].view(np.uint32), golden["add_lcg_expected"].view(np.uint32))
+
+
+def test_elementwise_add_full_size_properties(lib, gpu):
+    """2^28 elements: too large to compare everywhere cheaply, so check
+    commutativity, x + 0 == x, sampled slices against the oracle, and that
+    the guard elements after the end stay untouched."""
+    import torch
+    n = 1 << 28
+    g = torch.Generator(device="cuda").manual_seed(1)
+    x = torch.rand(n + 4, device="cuda", generator=g) * 2 - 1
+    y = torch.rand(n + 4, device="cuda", generator=g) * 2 - 1
+    out = torch.full((n + 4,), 3.0, device="cuda")
+    lib.elementwise_add_f32(x.data_ptr(), y.data_ptr(), out.data_ptr(), n, 0)
+    out2 = torch.empty(n, device="cuda")
+    lib.elementwise_add_f32(y.data_ptr(), x.data_ptr(), out2.data_ptr(), n, 0)
+    torch.cuda.synchronize()
+    assert torch.equal(out[:n].view(torch.int32), out2.view(torch.int32))
+    assert bool((out[n:] == 3.0).all())
+    for lo in (0, 4096 * 1000 + 1, n - 4096):
+        got = out[lo:lo + 4096].cpu().numpy()
+        want = oracle.elementwise_add(x[lo:lo + 4096].cpu().numpy(), y[lo:lo + 4096].cpu().numpy())
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    zero = torch.zeros(n, device="cuda")
+    lib.elementwise_add_f32(x.data_ptr(), zero.data_ptr(), out2.data_ptr(), n, 0)
+    torch.cuda.synchronize()
+    assert torch.equal(out2, x[:n])
+
+
+# ------------------------------------------------------------------------ sgemm
+@pytest.mark.parametrize("m,n,k", [(128, 128, 8), (256, 128, 32), (128, 256, 16), (256, 256, 64), (384, 128, 100), (128, 128, 0)])
+@pytest.mark.parametrize("small", [True, False])
+def test_sgemm_bit_exact(lib, gpu, m, n, k, small):
+    import torch
+    a, b, c0 = lcg_buffers([m * k, n * k, m * n], small=small)
+    dA, dB, dC = dev(a if k else np.zeros(4, np.float32)), dev(b if k else np.zeros(4, np.float32)), dev(c0)
+    lib.sgemm_nt(m, n, k, 1.5, -0.5, dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), 0)
+    torch.cuda.synchronize()
+    want = oracle.sgemm_nt(a, b, c0, 1.5, -0.5, m, n, k)
+    assert np.array_equal(dC.cpu().numpy().view(np.uint32), want.view(np.uint32))
+
+
+def test_sgemm_golden(lib, gpu, golden):
+    import torch
+    m, n, k = 256, 256, 64
+    a = ((np.arange(m * k, dtype=np.int64) * 7) % 11 - 5).astype(np.float32)
+    b = ((np.arange(n * k, dtype=np.int64) * 3) % 13 - 6).astype(np.float32)
+    c0 = (np.arange(m * n, dtype=np.int64) % 5).astype(np.float32)
+    dA, dB, dC = dev(a), dev(b), dev(c0)
+    lib.sgemm_nt(m, n, k, 1.5, -0.5, dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), 0)
+    torch.cuda.synchronize()
+    assert np.array_equal(dC.cpu().numpy(), golden["sgemm_int_256x256x64"])
+    m, n, k = 256, 128, 32
+    a, b, c0 = lcg_buffers([m * k, n * k, m * n], small=False)
+    dA, dB, dC = dev(a), dev(b), dev(c0)
+    lib.sgemm_nt(m, n, k, 1.5, -0.5, dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), 0)
+    torch.cuda.synchronize()
+    got = dC.cpu().numpy()
+    for (i, j), want in zip(golden["sgemm_lcg_samples"], golden["sgemm_lcg_expected"]):
+        assert got[i + j * m].view(np.uint32) == want.view(np.uint32)
+
+
+def test_sgemm_rejects_bad_shapes(lib, gpu):
+    with pytest.raises(lib.CuteB200Error) as e:
+        lib.sgemm_nt(100, 128, 8, 1.0, 0.0, 256, 256, 256, 0)
+    assert e.value.status == lib.ERR_INVALID_ARGUMENT and "multiple of the tile size" in e.value.message
+
+
+def test_sgemm_full_size_sampled(lib, gpu):
+    """4096^3 (the sgemm config): full-size run, outputs sampled against the
+    oracle's single-element form."""
+    import torch
+    n = 4096
+    rng = np.random.default_rng(2)
+    a, b, c0 = (rng.uniform(-1, 1, n * n).astype(np.float32) for _ in range(3))
+    dA, dB, dC = dev(a), dev(b), dev(c0)
+    lib.sgemm_nt(n, n, n, 1.5, 0.5, dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), 0)
+    torch.cuda.synchronize()
+    got = dC.cpu().numpy()
+    for i, j in [(0, 0), (4095, 4095), (127, 128), (128, 127), (1000, 3001), (2048, 64), (63, 4032)]:
+        want = np.float32(oracle.sgemm_nt_naive_elem(a, b, float(c0[i + j * n]), 1.5, 0.5, n, n, n, i, j))
+        assert got[i + j * n].view(np.uint32) == want.view(np.uint32), (i, j)
+
+
+# ------------------------------------------------------------------------- gemm
+GEMM_SHAPES = [(128, 128, 64), (256, 128, 96), (128, 256, 160), (256, 256, 256), (512, 512, 512), (128, 128, 32),
+               (384, 640, 1088)]
+
+
+@pytest.mark.parametrize("m,n,k", GEMM_SHAPES)
+@pytest.mark.parametrize("ab_name", ["f16", "bf16"])
+@pytest.mark.parametrize("cta_group,tile_n", [(1, 128), (1, 256), (2, 128), (2, 256), (0, 0)])
+def test_gemm_small_integers_bit_exact(lib, gpu, m, n, k, ab_name, cta_group, tile_n):
+    ab = lib.F16 if ab_name == "f16" else lib.BF16
+    a, b, _ = lcg_buffers([m * k, n * k, 0], small=True)
+    a_bits, b_bits = conv(lib, ab)(a.reshape(m, k)), conv(lib, ab)(b.reshape(n, k))
+    got = run_gemm(lib, a_bits, b_bits, ab, lib.F32, tile_n=tile_n, cta_group=cta_group)
+    want = oracle.gemm_tn(a_bits, b_bits, ab)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+@pytest.mark.parametrize("shape", [(128, 128, 64), (256, 128, 96), (128, 256, 160)])
+@pytest.mark.parametrize("ab_name", ["f16", "bf16"])
+def test_gemm_example_inputs_match_golden(lib, gpu, golden, shape, ab_name):
+    m, n, k = shape
+    ab = lib.F16 if ab_name == "f16" else lib.BF16
+    a = ((np.arange(m * k, dtype=np.int64) * 7 + 3) % 7 - 3).astype(np.float32).reshape(m, k)
+    b = ((np.arange(n * k, dtype=np.int64) * 5 + 1) % 5 - 2).astype(np.float32).reshape(n, k)
+    got = run_gemm(lib, conv(lib, ab)(a), conv(lib, ab)(b), ab, lib.F32)
+    assert np.array_equal(got, golden[f"tensorop_int_{m}x{n}x{k}"].astype(np.float32))
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 128, 96), (256, 256, 256), (512, 384, 2048)])
+@pytest.mark.parametrize("ab_name", ["f16", "bf16"])
+@pytest.mark.parametrize("cta_group", [1, 2])
+def test_gemm_random_within_reference_bound(lib, gpu, m, n, k, ab_name, cta_group):
+    ab = lib.F16 if ab_name == "f16" else lib.BF16
+    a, b, _ = lcg_buffers([m * k, n * k, 0], small=False)
+    a_bits, b_bits = conv(lib, ab)(a.reshape(m, k)), conv(lib, ab)(b.reshape(n, k))
+    got = run_gemm(lib, a_bits, b_bits, ab, lib.F32, cta_group=cta_group)
+    want = oracle.gemm_tn(a_bits, b_bits, ab)
+    allowed = tensor_core_bound(k, oracle.gemm_tn_abs(a_bits, b_bits, ab))
+    assert (np.abs(got.astype(np.float64) - want.astype(np.float64)) <= allowed).all()
+
+
+def test_gemm_config0_256_cubed_uniform_seed0(lib, gpu):
+    """tensorop_gemm 256^3, f16 uniform[-1, 1) seed 0, C zeros, alpha 1, beta 0."""
+    rng = np.random.default_rng(0)
+    a = oracle.f32_to_f16_bits(rng.uniform(-1, 1, (256, 256)).astype(np.float32))
+    b = oracle.f32_to_f16_bits(rng.uniform(-1, 1, (256, 256)).astype(np.float32))
+    got = run_gemm(lib, a, b, lib.F16, lib.F32)
+    want = oracle.gemm_tn(a, b, lib.F16)
+    assert (np.abs(got.astype(np.float64) - want) <= tensor_core_bound(256, oracle.gemm_tn_abs(a, b, lib.F16))).all()
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 1, 8), (100, 200, 72), (200, 136, 8), (129, 257, 520), (300, 520, 200), (128, 130, 64)])
+@pytest.mark.parametrize("cdt_name", ["f32", "bf16"])
+@pytest.mark.parametrize("cta_group", [1, 2])
+def test_gemm_ragged_shapes(lib, gpu, m, n, k, cdt_name, cta_group):
+    cdt = lib.F32 if cdt_name == "f32" else lib.BF16
+    a, b, _ = lcg_buffers([m * k, n * k, 0], small=True)
+    a_bits, b_bits = oracle.f32_to_bf16_bits(a.reshape(m, k)), oracle.f32_to_bf16_bits(b.reshape(n, k))
+    got = run_gemm(lib, a_bits, b_bits, lib.BF16, cdt, cta_group=cta_group)
+    want = oracle.gemm_tn(a_bits, b_bits, lib.BF16, cdt)
+    if cdt == lib.F32:
+        assert np.array_equal(got, want)
+    else:  # integer sums can exceed 8 significand bits: compare after the same rounding
+        assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("cdt_name", ["f32", "bf16"])
+@pytest.mark.parametrize("alpha,beta", [(1.5, -0.5), (0.0, 1.0), (2.0, 0.0), (1.0, 1.0)])
+def test_gemm_alpha_beta_epilogue(lib, gpu, cdt_name, alpha, beta):
+    cdt = lib.F32 if cdt_name == "f32" else lib.BF16
+    m, n, k = 256, 384, 128
+    a, b, c = lcg_buffers([m * k, n * k, m * n], small=True)
+    a_bits, b_bits = oracle.f32_to_f16_bits(a.reshape(m, k)), oracle.f32_to_f16_bits(b.reshape(n, k))
+    c0 = c.reshape(m, n) if cdt == lib.F32 else oracle.f32_to_bf16_bits(c.reshape(m, n))
+    got = run_gemm(lib, a_bits, b_bits, lib.F16, cdt, alpha, beta, c0=c0)
+    want = oracle.gemm_tn(a_bits, b_bits, lib.F16, cdt, alpha, beta, c_init=c0)
+    assert np.array_equal(got, want)
+
+
+def test_gemm_k_zero_and_write_only_c(lib, gpu):
+    m, n = 130, 70
+    c0 = np.full((m, n), np.float32(np.nan))
+    z = np.zeros((m, 0), np.uint16), np.zeros((n, 0), np.uint16)
+    got = run_gemm(lib, z[0], z[1], lib.F16, lib.F32, c0=c0)
+    assert not got.any()  # alpha 1, beta 0: C is never read, NaNs do not leak
+    c1 = np.arange(m * n, dtype=np.float32).reshape(m, n)
+    got = run_gemm(lib, z[0], z[1], lib.F16, lib.F32, 2.0, 0.5, c0=c1)
+    assert np.array_equal(got, np.float32(0.5) * c1)
+    # beta == 0 with prior NaNs in C and k > 0
+    a, b, _ = lcg_buffers([128 * 64, 128 * 64, 0], small=True)
+    a_bits, b_bits = oracle.f32_to_f16_bits(a.reshape(128, 64)), oracle.f32_to_f16_bits(b.reshape(128, 64))
+    got = run_gemm(lib, a_bits, b_bits, lib.F16, lib.F32, c0=np.full((128, 128), np.float32(np.nan)))
+    assert np.array_equal(got, oracle.gemm_tn(a_bits, b_bits, lib.F16))
+
+
+def test_gemm_rejects_bad_arguments(lib, gpu):
+    d = lib.gemm_desc(128, 128, 20, lib.F16, lib.F32)
+    with pytest.raises(lib.CuteB200Error) as e:
+        lib.gemm_tn(d, 256, 256, 256, 0)
+    assert e.value.status == lib.ERR_INVALID_ARGUMENT and "multiple of 8" in e.value.message
+    with pytest.raises(lib.CuteB200Error) as e:
+        lib.gemm_tn(lib.gemm_desc(128, 128, 64, lib.F16, lib.F32), 256 + 2, 256, 256, 0)
+    assert e.value.status == lib.ERR_MISALIGNED
+    with pytest.raises(lib.CuteB200Error) as e:
+        lib.gemm_tn(lib.gemm_desc(128, 128, 64, lib.F32, lib.F32), 256, 256, 256, 0)
+    assert e.value.status == lib.ERR_INVALID_ARGUMENT
+
+
+@pytest.mark.parametrize("m,n,k", [(1024, 1024, 1024), (2048, 2048, 2048), (8192, 128, 8192), (16384, 1024, 8192)])
+def test_runtime_gemm_bf16_normal_inputs(lib, gpu, m, n, k):
+    """The runtime_gemm sweep: bf16 in, bf16 out, normal(0, 0.02) seed 3.
+    Large shapes are checked on a band of rows (the oracle computes only those)."""
+    import torch
+    g = torch.Generator(device="cuda").manual_seed(3)
+    A = (torch.randn(m, k, device="cuda", generator=g) * 0.02).bfloat16()
+    B = (torch.randn(n, k, device="cuda", generator=g) * 0.02).bfloat16()
+    C = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+    lib.gemm_tn(lib.gemm_desc(m, n, k, lib.BF16, lib.BF16), A.data_ptr(), B.data_ptr(), C.data_ptr(), 0)
+    torch.cuda.synchronize()
+    assert lib.device_status() == (0, 0, 0, 0)
+    a_bits = A.view(torch.int16).cpu().numpy().view(np.uint16)
+    b_bits = B.view(torch.int16).cpu().numpy().view(np.uint16)
+    got = C.view(torch.int16).cpu().numpy().view(np.uint16)
+    bands = [(0, min(m, 256))] if m <= 1024 else [(0, 128), (m // 2 - 64, m // 2 + 64), (m - 128, m)]
+    for lo, hi in bands:
+        acc = oracle.gemm_tn(a_bits, b_bits, lib.BF16, rows=(lo, hi))[lo:hi]
+        mag = oracle.gemm_tn_abs(a_bits, b_bits, lib.BF16, rows=(lo, hi))[lo:hi]
+        diff = np.abs(oracle.bf16_bits_to_f32(got[lo:hi]).astype(np.float64) - acc.astype(np.float64))
+        # rounding the f32 result to bf16 costs half a unit; a result that lands
+        # on the other side of a tie costs a whole one
+        assert (diff <= tensor_core_bound(k, mag) + bf16_ulp(acc)).all()
+
+
+def test_gemm_full_size_properties(lib, gpu):
+    """8192^3 bf16: linearity in A (exact for a power-of-two scale) and
+    agreement of the two tilings on sampled rows."""
+    import torch
+    n = 8192
+    g = torch.Generator(device="cuda").manual_seed(3)
+    A = (torch.randn(n, n, device="cuda", generator=g) * 0.02).bfloat16()
+    B = (torch.randn(n, n, device="cuda", generator=g) * 0.02).bfloat16()
+    C1 = torch.empty(n, n, device="cuda", dtype=torch.float32)
+    C2 = torch.empty_like(C1)
+    lib.gemm_tn(lib.gemm_desc(n, n, n, lib.BF16, lib.F32), A.data_ptr(), B.data_ptr(), C1.data_ptr(), 0)
+    A2 = (A.float() * 2).bfloat16()
+    lib.gemm_tn(lib.gemm_desc(n, n, n, lib.BF16, lib.F32), A2.data_ptr(), B.data_ptr(), C2.data_ptr(), 0)
+    torch.cuda.synchronize()
+    assert torch.equal(C2, C1 * 2)  # scaling by two is exact at every step
+    lib.gemm_tn(lib.gemm_desc(n, n, n, lib.BF16, lib.F32, tile_n=128, cta_group=1), A.data_ptr(), B.data_ptr(), C2.data_ptr(), 0)
+    torch.cuda.synchronize()
+    assert torch.equal(C2, C1)  # same k order per output in every tiling
+    a_bits = A[4000:4016].view(torch.int16).cpu().numpy().view(np.uint16)
+    b_bits = B.view(torch.int16).cpu().numpy().view(np.uint16)
+    want = oracle.gemm_tn(a_bits, b_bits, lib.BF16)
+    mag = oracle.gemm_tn_abs(a_bits, b_bits, lib.BF16)
+    diff = np.abs(C1[4000:4016].cpu().numpy().astype(np.float64) - want)
+    assert (diff <= tensor_core_bound(n, mag)).all()
+
+
+# -------------------------------------------------------- launch by kernel name
+def test_launch_by_name_mirrors_the_reference_examples(lib, gpu, golden):
+    from cute_rs_b200 import CudaContext, DeviceArg, DType
+    from cute_rs_b200 import examples as ex
+    ctx = CudaContext.new(0)
+    # tensorop_gemm, f16 and bf16 (examples/tensorop_gemm.rs:167-186)
+    for ab in (DType.F16, DType.BF16):
+        cfg = ex.GemmConfig(256, 128, 96, ab=ab)
+        kernel = ex.tensorop_gemm(cfg)
+        launch, args, a, b = ex.tensorop_gemm_problem(cfg)
+        stats = kernel.run_cuda(ctx, launch, args)
+        assert stats.kernel_seconds > 0.0
+        assert np.array_equal(args[2].as_f32().reshape(256, 128), golden["tensorop_int_256x128x96"].astype(np.float32))
+    # runtime_gemm: one kernel, several sizes, then device-resident relaunch
+    # (tests/gpu.rs:212-241)
+    kernel = ex.runtime_gemm()
+    for m, n, k in [(128, 128, 32), (256, 128, 96), (128, 256, 160), (512, 512, 512)]:
+        launch, args, a, b = ex.runtime_gemm_problem(m, n, k)
+        ctx.launch(kernel, launch, args)
+        want = a.reshape(m, k).astype(np.int64) @ b.reshape(n, k).astype(np.int64).T
+        assert np.array_equal(args[2].as_f32().reshape(m, n), want.astype(np.float32))
+    launch, args, a, b = ex.runtime_gemm_problem(256, 256, 64)
+    ua, ub, uc = ctx.upload(args[0]), ctx.upload(args[1]), ctx.upload(args[2])
+    dargs = [DeviceArg.Buffer(ua), DeviceArg.Buffer(ub), DeviceArg.Buffer(uc), DeviceArg.Scalar(args[3]), DeviceArg.Scalar(args[4])]
+    for _ in range(3):
+        ctx.launch_async(kernel, launch, dargs)
+    ctx.synchronize()
+    ctx.download(uc, args[2])
+    want = a.reshape(256, 64).astype(np.int64) @ b.reshape(256, 64).astype(np.int64).T
+    assert np.array_equal(args[2].as_f32().reshape(256, 256), want.astype(np.float32))
+    # sgemm (examples/sgemm.rs:84-112) and elementwise add (examples/elementwise_add.rs:82-91)
+    launch, args, *_ = ex.sgemm_problem(256, 256, 64)
+    ex.sgemm(256, 256, 64).run_cuda(ctx, launch, args)
+    assert np.array_equal(args[2].as_f32(), golden["sgemm_int_256x256x64"])
+    from cute_rs_b200 import LaunchConfig
+    for kernel, grid, block in [(ex.elementwise_add_naive(), ex.naive_grid(), [256, 1, 1]),
+                                (ex.elementwise_add_tiled(), ex.tiled_grid(), [128, 1, 1])]:
+        args, a, b = ex.elementwise_add_problem()
+        kernel.run_cuda(ctx, LaunchConfig.new(grid, block), args)
+        assert np.array_equal(args[2].as_f32(), golden["add_int_300x512"])
+        assert np.array_equal(args[0].as_f32(), a) and np.array_equal(args[1].as_f32(), b)  # inputs untouched
+
+
+def test_launch_by_name_errors(lib, gpu):
+    from cute_rs_b200 import CudaContext, CudaError, KernelArg, LaunchConfig
+    from cute_rs_b200 import examples as ex
+    ctx = CudaContext.new(0)
+    kernel = ex.runtime_gemm()
+    launch, args, *_ = ex.runtime_gemm_problem(128, 128, 32)
+    args[4] = KernelArg.ScalarI32(40)
+    with pytest.raises(CudaError, match=r"argument 4 \(`k`\) must be a multiple of 32, got 40"):
+        ctx.launch(kernel, launch, args)
+    launch, args, *_ = ex.runtime_gemm_problem(128, 128, 32)
+    with pytest.raises(CudaError, match="needs at least"):
+        ctx.launch(kernel, LaunchConfig.new([2, 1, 1], [128, 1, 1]), args)
+    t = ex.tensorop_gemm(ex.GemmConfig.new(128, 128, 64))
+    launch, args, *_ = ex.tensorop_gemm_problem(ex.GemmConfig.new(128, 128, 32))
+    with pytest.raises(CudaError, match=r"argument 0 \(`a`\) needs at least 8192 elements, got 4096"):
+        ctx.launch(t, launch, args)
