@@ -151,6 +151,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--skip-extras", action="store_true", help="skip cpu_baseline / e2e / secondary kernels (profiling runs)")
+    ap.add_argument("--only", choices=["add", "sgemm"], help="run just this secondary kernel (for ncu captures) and exit")
+    ap.add_argument("--log2n", type=int, default=28, help="--only add: log2 of the element count")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":
@@ -171,6 +173,11 @@ def main():
     lib.init(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    if args.only:
+        res = bench_add(lib, torch, peaks(), 1 << args.log2n) if args.only == "add" else bench_sgemm(lib, torch)
+        print(json.dumps(res))
+        return
 
     w = workload(world)
     M, N, K = w["m"], w["n"], w["k"]
@@ -291,8 +298,7 @@ def main():
         dist.destroy_process_group()
 
 
-def bench_add(lib, torch, pk):
-    n = 1 << 28
+def bench_add(lib, torch, pk, n=1 << 28):
     g = torch.Generator(device="cuda").manual_seed(1)
     x = torch.rand(n, device="cuda", generator=g) * 2 - 1
     y = torch.rand(n, device="cuda", generator=g) * 2 - 1
@@ -309,7 +315,7 @@ def bench_add(lib, torch, pk):
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / 20
     gbs = 12.0 * n / ms / 1e6
-    return {"workload": "elementwise_add f32 2^28 elements, uniform[-1,1) seed 1 (3 x 1 GiB, larger than L2)",
+    return {"workload": f"elementwise_add f32 {n} elements, uniform[-1,1) seed 1 (3 x {4 * n / 2 ** 30:.2f} GiB, larger than L2)",
             "gbs": gbs, "ms": ms, "bound": "hbm", "peak": pk["hbm_gbs"], "frac": gbs / pk["hbm_gbs"],
             "peak_kind": f"hbm_gbs ({pk['_source']})", "frac_of_nominal_8000": gbs / 8000.0,
             "algorithmic_bytes_per_launch": 12 * n}

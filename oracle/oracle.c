@@ -36,6 +36,11 @@ enum { ORACLE_F16 = 0, ORACLE_BF16 = 1, ORACLE_F32 = 2 };
 static inline uint32_t f32_bits(float x) { uint32_t b; memcpy(&b, &x, 4); return b; }
 static inline float bits_f32(uint32_t b) { float x; memcpy(&x, &b, 4); return x; }
 
+/* The NaN a single-precision PTX instruction returns: the simulator maps
+ * every NaN result of an f32 add, mul or fma to the canonical 0x7fffffff
+ * (ptx_nan, src/sim/float.rs:416-428; applied at src/sim/exec.rs:351, 1229). */
+static inline float ptx_nan_f32(float r) { return r != r ? bits_f32(0x7fffffffu) : r; }
+
 /* bf16 -> f32: the 16 bits become the high half.  src/value.rs:88-90 */
 static inline float bf16_to_f32(uint16_t h) { return bits_f32((uint32_t)h << 16); }
 
@@ -48,6 +53,11 @@ static inline uint16_t f32_to_bf16(float x) {
     if (x != x) return high | 0x40;
     return (uint16_t)(high + ((low > 0x8000u || (low == 0x8000u && (high & 1))) ? 1 : 0));
 }
+
+/* f32 -> bf16 as a kernel's own narrowing conversion does it: the same
+ * rounding, but a NaN becomes the canonical 0x7fff (cast, src/sim/exec.rs:
+ * 430-449). */
+static inline uint16_t f32_to_bf16_device(float x) { return x != x ? (uint16_t)0x7fff : f32_to_bf16(x); }
 
 /* f32 -> f16, round to nearest even with subnormals, overflow to infinity and
  * NaN payload kept.  src/value.rs:101-134 */
@@ -131,7 +141,7 @@ ORACLE_API int oracle_num_threads(void) {
  * (examples/elementwise_add.rs:66-78). */
 ORACLE_API void oracle_elementwise_add_f32(const float *x, const float *y, float *out, size_t n) {
 #pragma omp parallel for schedule(static)
-    for (size_t i = 0; i < n; i++) out[i] = x[i] + y[i];
+    for (size_t i = 0; i < n; i++) out[i] = ptx_nan_f32(x[i] + y[i]);
 }
 
 /* ------------------------------------------------------------------------ */
@@ -144,9 +154,9 @@ ORACLE_API void oracle_elementwise_add_f32(const float *x, const float *y, float
  * simulator (src/sim/exec.rs:342-351).  volatile keeps the compiler from
  * contracting them into an fma. */
 static inline float epilogue(float alpha, float acc, float beta, float c_old) {
-    volatile float p = alpha * acc;
-    volatile float q = beta * c_old;
-    return p + q;
+    volatile float p = ptx_nan_f32(alpha * acc);
+    volatile float q = ptx_nan_f32(beta * c_old);
+    return ptx_nan_f32(p + q);
 }
 
 /* ------------------------------------------------------------------------ */
@@ -198,7 +208,8 @@ static inline float load_ab(const void *p, int dtype, size_t idx) {
  *   C: (M, N) row-major, f32 or bf16.
  * With alpha == 1 and beta == 0 the accumulator is stored as is and C is
  * never read, like tensorop_gemm's epilogue (examples/tensorop_gemm.rs:161-162).
- * A bf16 C is the f32 result rounded to nearest even (src/value.rs:92-99).
+ * A bf16 C is the f32 result rounded to nearest even, NaN -> 0x7fff (the
+ * kernel-side cast, src/sim/exec.rs:430-449; rounding as src/value.rs:92-99).
  * Rows [row_begin, row_end) of C are produced; pass 0, M for all of them.
  * Returns 0, or -1 for an unsupported dtype. */
 ORACLE_API int oracle_gemm_tn(int ab_dtype, int c_dtype, size_t M, size_t N, size_t K, const void *A,
@@ -246,7 +257,7 @@ ORACLE_API int oracle_gemm_tn(int ab_dtype, int c_dtype, size_t M, size_t N, siz
                             c[idx] = plain ? v : epilogue(alpha, v, beta, c[idx]);
                         } else {
                             uint16_t *c = (uint16_t *)C;
-                            c[idx] = f32_to_bf16(plain ? v : epilogue(alpha, v, beta, bf16_to_f32(c[idx])));
+                            c[idx] = f32_to_bf16_device(plain ? v : epilogue(alpha, v, beta, bf16_to_f32(c[idx])));
                         }
                     }
             }
@@ -370,7 +381,8 @@ ORACLE_API int oracle_sgemm_nt(size_t M, size_t N, size_t K, float alpha, float 
                 for (size_t j = 0; j < SG_NR; j++)
                     for (size_t i = 0; i < SG_MR; i++) {
                         size_t idx = (ib * SG_MR + i) + (jb * SG_NR + j) * M;
-                        C[idx] = epilogue(alpha, acc[j * SG_MR + i], beta, C[idx]);
+                        /* a NaN accumulator is the canonical one: every fma step maps NaN to it */
+                        C[idx] = epilogue(alpha, ptx_nan_f32(acc[j * SG_MR + i]), beta, C[idx]);
                     }
             }
     }
@@ -396,6 +408,6 @@ ORACLE_API float oracle_gemm_tn_naive_elem(int ab_dtype, size_t K, const void *A
 ORACLE_API float oracle_sgemm_nt_naive_elem(size_t M, size_t N, size_t K, float alpha, float beta,
                                             const float *A, const float *B, float c_old, size_t i, size_t j) {
     float acc = 0.0f;
-    for (size_t kk = 0; kk < K; kk++) acc = fmaf(A[i + kk * M], B[j + kk * N], acc);
+    for (size_t kk = 0; kk < K; kk++) acc = ptx_nan_f32(fmaf(A[i + kk * M], B[j + kk * N], acc));
     return epilogue(alpha, acc, beta, c_old);
 }

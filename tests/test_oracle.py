@@ -119,3 +119,23 @@ def test_elementwise_add(golden):
     tiny = np.array([1e-45, 2e-45], np.float32)
     assert np.array_equal(oracle.elementwise_add(tiny, tiny), tiny + tiny) and (tiny + tiny)[0] != 0
     assert oracle.elementwise_add(np.zeros(0, np.float32), np.zeros(0, np.float32)).size == 0
+
+
+def test_nan_results_are_the_canonical_ptx_nan():
+    # inf + -inf, and NaN operands of any payload or sign (src/sim/float.rs:416-428)
+    x = np.array([np.inf, -np.inf, 1.0], np.float32)
+    y = np.array([-np.inf, np.inf, 0.0], np.float32)
+    y[2:] = np.array([0xFFC12345], np.uint32).view(np.float32)
+    assert list(oracle.elementwise_add(x, y).view(np.uint32)) == [0x7FFFFFFF] * 3
+    m = n = 64
+    k = 4
+    a = np.ones(m * k, np.float32)
+    b = np.ones(n * k, np.float32)
+    a[5] = np.array([0xFFC00001], np.uint32).view(np.float32)[0]  # a NaN operand in row 5, k = 0
+    c = oracle.sgemm_nt(a, b, np.zeros(m * n, np.float32), 1.0, 1.0, m, n, k)
+    assert (c.reshape(n, m)[:, 5].view(np.uint32) == 0x7FFFFFFF).all()
+    # a kernel-side narrowing to bf16 maps NaN to 0x7fff (src/sim/exec.rs:430-449)
+    z = np.zeros((8, 8), np.uint16)
+    c0 = np.full((8, 8), np.float32(np.nan))
+    out = oracle.gemm_tn(z, z, oracle.BF16, oracle.BF16, alpha=1.0, beta=1.0, c_init=oracle.f32_to_bf16_bits(c0))
+    assert (out == 0x7FFF).all()
