@@ -14,10 +14,14 @@
 //            N = BN, K = 16, four per stage) into a TMEM accumulator and
 //            releases the stage with tcgen05.commit on its `empty` mbarrier.
 //            Also owns the TMEM allocation.
-//   warps 2-5  epilogue: tcgen05.ld of the finished accumulator (each warp
-//            its own 32 TMEM lanes), alpha/beta, conversion, global stores.
-// The accumulator is double buffered in TMEM (2 x BN columns) so the epilogue
-// of tile i overlaps the main loop of tile i+1.
+//   warps 2-9  epilogue: tcgen05.ld of the finished accumulator (each warp
+//            its own 32 TMEM lanes and every other 32-column chunk),
+//            alpha/beta, conversion, global stores.
+// Each CTA keeps one (MH = 1) or two (MH = 2) 128-row accumulators of BN f32
+// columns in TMEM.  When two sets fit in the 512 columns they are double
+// buffered and the epilogue of tile i overlaps the main loop of tile i+1; the
+// largest tile (256 rows x 256 columns per CTA) fills TMEM on its own, and the
+// next tile's MMAs restart half by half as the epilogue drains each half.
 //
 // With CTA_GROUP == 2 two CTAs of a cluster work on one 256-row tile: each
 // loads its own 128 rows of A and its own half of the B rows, the leader CTA
@@ -45,7 +49,7 @@ namespace {
 constexpr int BM = 128;        // rows of C per CTA = TMEM lanes
 constexpr int BK = 64;         // k per stage: 64 x 2 B = one 128-byte swizzle row
 constexpr int UMMA_K = 16;     // k per tcgen05.mma for 16-bit inputs
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 320;  // warp 0 TMA, warp 1 MMA + TMEM, warps 2-9 epilogue
 constexpr uint32_t RING_BYTES = 224 * 1024;
 constexpr uint32_t BAR_BYTES = 256;
 constexpr uint64_t WAIT_LIMIT_NS = 4ull * 1000 * 1000 * 1000;
@@ -53,17 +57,25 @@ constexpr uint64_t WAIT_LIMIT_NS = 4ull * 1000 * 1000 * 1000;
 // Report codes written to the status word.
 enum : uint32_t { WHERE_PRODUCER = 1, WHERE_MMA_FULL = 2, WHERE_MMA_TMEM = 3, WHERE_EPILOGUE = 4, WHERE_DRAIN = 5 };
 
-template <int CTA_GROUP, int BN>
+// CTA_GROUP: CTAs per MMA (1, or 2 = a cluster pair).  BN: columns of C per
+// tile (the MMA's N).  MH: 128-row accumulators per CTA (1 or 2); with MH == 2
+// a CTA owns 256 rows of C, reuses every B block for two MMAs and so moves a
+// quarter less operand data per flop, at the price of a single-buffered
+// accumulator when BN == 256 (2 x 256 columns fill the 512 columns of TMEM).
+template <int CTA_GROUP, int BN, int MH>
 struct Cfg {
+    static constexpr int A_ROWS = BM * MH;         // A rows this CTA loads per stage
     static constexpr int B_ROWS = BN / CTA_GROUP;  // B rows this CTA loads per stage
-    static constexpr uint32_t A_BYTES = BM * BK * 2;
+    static constexpr uint32_t A_BYTES = A_ROWS * BK * 2;
     static constexpr uint32_t B_BYTES = B_ROWS * BK * 2;
     static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int STAGES = RING_BYTES / STAGE_BYTES;
-    static constexpr uint32_t TMEM_COLS = 2 * BN;
+    static constexpr int ACC_COLS = MH * BN;                        // TMEM columns of one accumulator set
+    static constexpr int ACC_BUFS = (2 * ACC_COLS <= 512) ? 2 : 1;  // double buffered when it fits
+    static constexpr uint32_t TMEM_COLS = (ACC_COLS * ACC_BUFS <= 256) ? 256 : 512;
     static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + BAR_BYTES;
     static_assert(STAGES >= 2 && STAGES <= 12, "ring depth");
-    static_assert(TMEM_COLS == 256 || TMEM_COLS == 512, "TMEM columns must be a power of two");
+    static_assert(ACC_COLS * ACC_BUFS <= 512, "accumulators exceed TMEM");
 };
 
 struct GemmParams {
@@ -72,8 +84,9 @@ struct GemmParams {
     float alpha, beta;
     uint32_t idesc;
     int m_tiles, n_tiles, group_m;
-    int c_vec_ok;  // C base and row pitch allow 16-byte accesses
+    int c_vec_ok;  // C base and row pitch allow 16-byte (1) or 32-byte (2) accesses
     int debug;     // timing experiments only: bit 0 skips the TMA loads, bit 1 skips the stores
+    int stage_limit;  // timing experiments only: use this many ring stages (0 = all)
     uint32_t *status;
 };
 
@@ -139,7 +152,12 @@ __device__ __forceinline__ void store_chunk(const GemmParams &p, int row, int co
     };
     if constexpr (!C_BF16) {
         float *crow = reinterpret_cast<float *>(p.C) + size_t(row) * p.ldc + col0;
-        if (p.c_vec_ok && col0 + 32 <= p.N) {
+        if (p.c_vec_ok == 2 && plain && col0 + 32 <= p.N) {
+#pragma unroll
+            for (int g = 0; g < 4; g++)
+                ptx::st_global_v8(crow + 8 * g, v[8 * g], v[8 * g + 1], v[8 * g + 2], v[8 * g + 3], v[8 * g + 4],
+                                  v[8 * g + 5], v[8 * g + 6], v[8 * g + 7]);
+        } else if (p.c_vec_ok && col0 + 32 <= p.N) {
 #pragma unroll
             for (int g = 0; g < 8; g++) {
                 float4 o;
@@ -160,7 +178,16 @@ __device__ __forceinline__ void store_chunk(const GemmParams &p, int row, int co
         }
     } else {
         __nv_bfloat16 *crow = reinterpret_cast<__nv_bfloat16 *>(p.C) + size_t(row) * p.ldc + col0;
-        if (p.c_vec_ok && col0 + 32 <= p.N) {
+        if (p.c_vec_ok == 2 && plain && col0 + 32 <= p.N) {
+            uint32_t w[16];
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+                const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+                w[j] = *reinterpret_cast<const uint32_t *>(&h);
+            }
+            ptx::st_global_v8(crow, w[0], w[1], w[2], w[3], w[4], w[5], w[6], w[7]);
+            ptx::st_global_v8(crow + 16, w[8], w[9], w[10], w[11], w[12], w[13], w[14], w[15]);
+        } else if (p.c_vec_ok && col0 + 32 <= p.N) {
 #pragma unroll
             for (int g = 0; g < 4; g++) {
                 float f[8];
@@ -195,21 +222,21 @@ __device__ __forceinline__ void store_chunk(const GemmParams &p, int row, int co
     }
 }
 
-template <int CTA_GROUP, int BN, bool C_BF16>
+template <int CTA_GROUP, int BN, int MH, bool C_BF16>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
     gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                    const GemmParams p) {
-    using C = Cfg<CTA_GROUP, BN>;
+    using C = Cfg<CTA_GROUP, BN, MH>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = ptx::smem_u32(smem_raw);
     const uint32_t ring = (raw + 1023u) & ~1023u;  // swizzle atoms need 1024-byte alignment
     const uint32_t bars = ring + C::STAGES * C::STAGE_BYTES;
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (C::STAGES + s); };
-    auto tfull_bar = [&](int a) { return bars + 8u * (2 * C::STAGES + a); };
-    auto tempty_bar = [&](int a) { return bars + 8u * (2 * C::STAGES + 2 + a); };
-    const uint32_t drain_bar = bars + 8u * (2 * C::STAGES + 4);
-    uint8_t *tail = smem_raw + (bars - raw) + 8u * (2 * C::STAGES + 5);
+    auto tfull_bar = [&](int buf) { return bars + 8u * (2 * C::STAGES + buf); };
+    auto tempty_bar = [&](int buf, int h) { return bars + 8u * (2 * C::STAGES + 2 + buf * 2 + h); };
+    const uint32_t drain_bar = bars + 8u * (2 * C::STAGES + 6);
+    uint8_t *tail = smem_raw + (bars - raw) + 8u * (2 * C::STAGES + 7);
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(tail);
     volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(tail + 4);
 
@@ -219,15 +246,17 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     const int num_clusters = gridDim.x / CTA_GROUP;
     const int num_tiles = p.m_tiles * p.n_tiles;
     const int k_blocks = (p.K + BK - 1) / BK;
+    const int nstages = (p.stage_limit > 0 && p.stage_limit < C::STAGES) ? p.stage_limit : C::STAGES;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; s++) {
             ptx::mbar_init(full_bar(s), 1);
             ptx::mbar_init(empty_bar(s), 1);
         }
-        for (int a = 0; a < 2; a++) {
-            ptx::mbar_init(tfull_bar(a), 1);
-            ptx::mbar_init(tempty_bar(a), 4 * CTA_GROUP);  // one arrival per epilogue warp of the pair
+        for (int buf = 0; buf < 2; buf++) {
+            ptx::mbar_init(tfull_bar(buf), 1);
+            for (int h = 0; h < 2; h++)
+                ptx::mbar_init(tempty_bar(buf, h), 8 * CTA_GROUP);  // one arrival per epilogue warp of the pair
         }
         ptx::mbar_init(drain_bar, 1);
         *abort_flag = 0u;
@@ -257,7 +286,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             bool ok = true;
             for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
                 const TileCoord tc = tile_coord(t, p);
-                const int row_a = (tc.tm * CTA_GROUP + int(rank)) * BM;
+                const int row_a = (tc.tm * CTA_GROUP + int(rank)) * C::A_ROWS;
                 const int row_b = tc.tn * BN + int(rank) * C::B_ROWS;
                 for (int kb = 0; kb < k_blocks; kb++) {
                     if (!wait_bar(empty_bar(s), ph ^ 1u, abort_flag, p.status, WHERE_PRODUCER, uint32_t(s))) {
@@ -282,7 +311,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                     }
                     filled |= 1u << s;
                     filled_parity = (filled_parity & ~(1u << s)) | (ph << s);
-                    if (++s == C::STAGES) {
+                    if (++s == nstages) {
                         s = 0;
                         ph ^= 1u;
                     }
@@ -308,39 +337,49 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             bool ok = true, issued = false;
             int it = 0;
             for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, it++) {
-                const int acc = it & 1;
-                const uint32_t aph = uint32_t(it >> 1) & 1u;
-                if (!wait_bar(tempty_bar(acc), aph ^ 1u, abort_flag, p.status, WHERE_MMA_TMEM, uint32_t(acc))) {
-                    ok = false;
-                    break;
-                }
-                ptx::tc_fence_after();
-                const uint32_t d_tmem = tmem_base + uint32_t(acc * BN);
-                for (int kb = 0; kb < k_blocks; kb++) {
+                const int buf = it % C::ACC_BUFS;
+                const uint32_t aph = uint32_t(it / C::ACC_BUFS) & 1u;
+                const uint32_t d_tmem = tmem_base + uint32_t(buf * C::ACC_COLS);
+                for (int kb = 0; kb < k_blocks && ok; kb++) {
                     if (!wait_bar(full_bar(s), ph, abort_flag, p.status, WHERE_MMA_FULL, uint32_t(s))) {
                         ok = false;
                         break;
                     }
                     ptx::tc_fence_after();
                     const uint32_t a_src = ring + uint32_t(s) * C::STAGE_BYTES;
-                    const uint64_t a_desc = sw128_desc(a_src), b_desc = sw128_desc(a_src + C::A_BYTES);
+                    const uint64_t b_desc = sw128_desc(a_src + C::A_BYTES);
 #pragma unroll
-                    for (int j = 0; j < BK / UMMA_K; j++) {
-                        // 16 elements of k = 32 bytes = 2 units of the address field
-                        ptx::umma_f16<CTA_GROUP>(d_tmem, a_desc + 2u * j, b_desc + 2u * j, p.idesc,
-                                                 (kb > 0 || j > 0) ? 1u : 0u);
+                    for (int h = 0; h < MH; h++) {
+                        if (kb == 0) {
+                            // The epilogue must have drained this half of the buffer
+                            // (a fresh barrier passes at once).
+                            if (!wait_bar(tempty_bar(buf, h), aph ^ 1u, abort_flag, p.status, WHERE_MMA_TMEM,
+                                          uint32_t(buf * 2 + h))) {
+                                ok = false;
+                                break;
+                            }
+                            ptx::tc_fence_after();
+                        }
+                        const uint64_t a_desc = sw128_desc(a_src + uint32_t(h) * (BM * BK * 2));
+#pragma unroll
+                        for (int j = 0; j < BK / UMMA_K; j++) {
+                            // 16 elements of k = 32 bytes = 2 units of the address field
+                            ptx::umma_f16<CTA_GROUP>(d_tmem + uint32_t(h * BN), a_desc + 2u * j, b_desc + 2u * j, p.idesc,
+                                                     (kb > 0 || j > 0) ? 1u : 0u);
+                        }
+                        issued = true;
                     }
-                    issued = true;
+                    if (!ok) break;
                     ptx::umma_commit<CTA_GROUP>(empty_bar(s));
                     if constexpr (CTA_GROUP == 2) ptx::umma_commit<CTA_GROUP>(ptx::mapa(empty_bar(s), 1));
-                    if (++s == C::STAGES) {
+                    if (++s == nstages) {
                         s = 0;
                         ph ^= 1u;
                     }
                 }
                 if (!ok) break;
-                ptx::umma_commit<CTA_GROUP>(tfull_bar(acc));
-                if constexpr (CTA_GROUP == 2) ptx::umma_commit<CTA_GROUP>(ptx::mapa(tfull_bar(acc), 1));
+                ptx::umma_commit<CTA_GROUP>(tfull_bar(buf));
+                if constexpr (CTA_GROUP == 2) ptx::umma_commit<CTA_GROUP>(ptx::mapa(tfull_bar(buf), 1));
             }
             if (!ok && issued) {
                 // Giving up: wait (bounded) until the tensor core is done with
@@ -354,44 +393,63 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         __syncwarp();
     } else {
         // ------------------------------------------------------------ epilogue
-        const uint32_t q = uint32_t(warp) & 3u;  // the TMEM lane quarter this warp may read
+        // Eight warps: warp w reads TMEM lane quarter w % 4 (the only one it may
+        // address) and, of every 128-row half, the 32-column chunks of parity e.
+        const uint32_t q = uint32_t(warp) & 3u;
+        const int e = (warp - 2) >> 2;
+        constexpr int CH = BN / 64;       // chunks per half per warp
+        constexpr int ITEMS = MH * CH;    // even
         const bool plain = (p.alpha == 1.0f && p.beta == 0.0f);
         bool ok = true;
         int it = 0;
         for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, it++) {
             const TileCoord tc = tile_coord(t, p);
-            const int acc = it & 1;
-            const uint32_t aph = uint32_t(it >> 1) & 1u;
-            if (k_blocks > 0) {
-                if (!wait_bar(tfull_bar(acc), aph, abort_flag, p.status, WHERE_EPILOGUE, uint32_t(acc))) {
+            const int buf = it % C::ACC_BUFS;
+            const uint32_t aph = uint32_t(it / C::ACC_BUFS) & 1u;
+            const bool have_acc = k_blocks > 0;
+            if (have_acc) {
+                if (!wait_bar(tfull_bar(buf), aph, abort_flag, p.status, WHERE_EPILOGUE, uint32_t(buf))) {
                     ok = false;
                     break;
                 }
                 ptx::tc_fence_after();
             }
-            const int row = (tc.tm * CTA_GROUP + int(rank)) * BM + int(q) * 32 + lane;
-            const uint32_t taddr = tmem_base + ((q * 32u) << 16) + uint32_t(acc * BN);
-#pragma unroll 1
-            for (int chunk = 0; chunk < BN / 32; chunk++) {
-                uint32_t v[32];
-                if (k_blocks > 0) {
-                    ptx::tmem_ld_32x32(taddr + uint32_t(chunk * 32), v);
-                    ptx::tmem_ld_wait();
+            const int row0 = (tc.tm * CTA_GROUP + int(rank)) * C::A_ROWS + int(q) * 32 + lane;
+            const uint32_t taddr0 = tmem_base + ((q * 32u) << 16) + uint32_t(buf * C::ACC_COLS);
+            auto col_of = [&](int i) { return ((i % CH) * 2 + e) * 32; };
+            auto load = [&](int i, uint32_t(&v)[32]) {
+                if (have_acc) {
+                    ptx::tmem_ld_32x32(taddr0 + uint32_t((i / CH) * BN + col_of(i)), v);
                 } else {
 #pragma unroll
                     for (int j = 0; j < 32; j++) v[j] = 0u;
                 }
-                if (chunk == BN / 32 - 1 && k_blocks > 0) {
-                    // All of this warp's reads of the accumulator are done:
-                    // hand the TMEM buffer back before the last stores.
+            };
+            // Item i has landed in v: release its half if it was this warp's last
+            // read of it, then convert and store.
+            auto finish = [&](int i, uint32_t(&v)[32]) {
+                if (have_acc && (i % CH) == CH - 1) {
                     ptx::tc_fence_before();
                     __syncwarp();
                     if (lane == 0) {
-                        if constexpr (CTA_GROUP == 1) ptx::mbar_arrive(tempty_bar(acc));
-                        else ptx::mbar_arrive_cluster(ptx::mapa(tempty_bar(acc), 0));
+                        if constexpr (CTA_GROUP == 1) ptx::mbar_arrive(tempty_bar(buf, i / CH));
+                        else ptx::mbar_arrive_cluster(ptx::mapa(tempty_bar(buf, i / CH), 0));
                     }
                 }
-                if (!(p.debug & 2)) store_chunk<C_BF16>(p, row, tc.tn * BN + chunk * 32, v, plain);
+                if (!(p.debug & 2)) store_chunk<C_BF16>(p, row0 + (i / CH) * BM, tc.tn * BN + col_of(i), v, plain);
+            };
+            // Two register buffers: the TMEM read of the next chunk is in flight
+            // while the current one is converted and stored.
+            uint32_t va[32], vb[32];
+            load(0, va);
+#pragma unroll 1
+            for (int i = 0; i < ITEMS; i += 2) {
+                if (have_acc) ptx::tmem_ld_wait(va);
+                load(i + 1, vb);
+                finish(i, va);
+                if (have_acc) ptx::tmem_ld_wait(vb);
+                if (i + 2 < ITEMS) load(i + 2, va);
+                finish(i + 1, vb);
             }
         }
     }
@@ -478,11 +536,12 @@ cute_b200_status make_tensor_map(CUtensorMap *tm, uint64_t base, int dtype, int 
     return CUTE_B200_OK;
 }
 
-template <int CTA_GROUP, int BN, bool C_BF16>
+template <int CTA_GROUP, int BN, int MH, bool C_BF16>
 cute_b200_status launch(const CUtensorMap &tmA, const CUtensorMap &tmB, GemmParams p, int sm_count,
                         cudaStream_t stream) {
-    using C = Cfg<CTA_GROUP, BN>;
-    p.m_tiles = (p.M + BM * CTA_GROUP - 1) / (BM * CTA_GROUP);
+    using C = Cfg<CTA_GROUP, BN, MH>;
+    const int tile_rows = BM * MH * CTA_GROUP;
+    p.m_tiles = (p.M + tile_rows - 1) / tile_rows;
     p.n_tiles = (p.N + BN - 1) / BN;
     const long long tiles = (long long)p.m_tiles * p.n_tiles;
     int clusters = sm_count / CTA_GROUP;
@@ -491,6 +550,7 @@ cute_b200_status launch(const CUtensorMap &tmA, const CUtensorMap &tmB, GemmPara
     // column so that a wave of CTAs covers a near-square patch of C.
     int gm = 1;
     while (gm * gm * 2 <= clusters) gm *= 2;
+    if (p.group_m > 0) gm = p.group_m;  // caller's override
     p.group_m = gm < p.m_tiles ? gm : p.m_tiles;
     if (p.group_m < 1) p.group_m = 1;
 
@@ -506,29 +566,63 @@ cute_b200_status launch(const CUtensorMap &tmA, const CUtensorMap &tmB, GemmPara
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    CB_CUDA(cudaLaunchKernelEx(&cfg, gemm_tn_kernel<CTA_GROUP, BN, C_BF16>, tmA, tmB, p));
+    CB_CUDA(cudaLaunchKernelEx(&cfg, gemm_tn_kernel<CTA_GROUP, BN, MH, C_BF16>, tmA, tmB, p));
     count_launch();
     return CUTE_B200_OK;
 }
 
-template <int CTA_GROUP, int BN, bool C_BF16>
+template <int CTA_GROUP, int BN, int MH, bool C_BF16>
 cute_b200_status set_smem_limit() {
-    CB_CUDA(cudaFuncSetAttribute(gemm_tn_kernel<CTA_GROUP, BN, C_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 Cfg<CTA_GROUP, BN>::SMEM_BYTES));
+    CB_CUDA(cudaFuncSetAttribute(gemm_tn_kernel<CTA_GROUP, BN, MH, C_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 Cfg<CTA_GROUP, BN, MH>::SMEM_BYTES));
     return CUTE_B200_OK;
+}
+
+// Every (cta_group, tile_n, rows-per-CTA, C type) the library instantiates.
+#define CB_GEMM_VARIANTS(X) \
+    X(1, 128, 1, false) X(1, 128, 1, true) X(1, 256, 1, false) X(1, 256, 1, true) \
+    X(2, 128, 1, false) X(2, 128, 1, true) X(2, 256, 1, false) X(2, 256, 1, true) \
+    X(1, 128, 2, false) X(1, 128, 2, true) X(1, 256, 2, false) X(1, 256, 2, true) \
+    X(2, 128, 2, false) X(2, 128, 2, true) X(2, 256, 2, false) X(2, 256, 2, true)
+
+// Relative mainloop efficiency of a tiling, measured on 8192^3 bf16 (the 512 x 256
+// pair tile is the reference point); used only to rank candidates.
+double tiling_efficiency(int group, int bn, int mh) {
+    double e = 1.0;
+    if (group == 1) e *= (mh == 2 ? 0.90 : 0.86);
+    else if (mh == 1) e *= 0.92;
+    if (bn == 128) e *= (mh == 2 ? 0.85 : 0.72);
+    return e;
+}
+
+// Pick the tiling with the smallest estimated time: whole waves of tiles over
+// the clusters that fit, divided by the tiling's efficiency.
+void choose_tiling(int m, int n, int sm_count, int want_group, int want_bn, int want_mh, int *group, int *bn, int *mh) {
+    double best = 1e300;
+    for (int g = 1; g <= 2; g++)
+        for (int b = 128; b <= 256; b += 128)
+            for (int h = 1; h <= 2; h++) {
+                if ((want_group && g != want_group) || (want_bn && b != want_bn) || (want_mh && h != want_mh)) continue;
+                const long long rows = 128LL * g * h;
+                const long long tiles = ((m + rows - 1) / rows) * ((n + b - 1) / b);
+                const long long clusters = sm_count / g;
+                const long long waves = (tiles + clusters - 1) / clusters;
+                const double t = double(waves) * double(rows) * b / (g * tiling_efficiency(g, b, h));
+                if (t < best) {
+                    best = t;
+                    *group = g;
+                    *bn = b;
+                    *mh = h;
+                }
+            }
 }
 
 }  // namespace
 
 cute_b200_status gemm_tn_init(const DeviceState &) {
-    CB_TRY((set_smem_limit<1, 128, false>()));
-    CB_TRY((set_smem_limit<1, 128, true>()));
-    CB_TRY((set_smem_limit<1, 256, false>()));
-    CB_TRY((set_smem_limit<1, 256, true>()));
-    CB_TRY((set_smem_limit<2, 128, false>()));
-    CB_TRY((set_smem_limit<2, 128, true>()));
-    CB_TRY((set_smem_limit<2, 256, false>()));
-    CB_TRY((set_smem_limit<2, 256, true>()));
+#define CB_SET(G, N_, H, BF) CB_TRY((set_smem_limit<G, N_, H, BF>()));
+    CB_GEMM_VARIANTS(CB_SET)
+#undef CB_SET
     return CUTE_B200_OK;
 }
 
@@ -545,6 +639,8 @@ cute_b200_status gemm_tn(const cute_b200_gemm_desc &d, uint64_t a, uint64_t b, u
         return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "gemm_tn: tile_n must be 0, 128 or 256, got %d", d.tile_n);
     if (d.cta_group < 0 || d.cta_group > 2)
         return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "gemm_tn: cta_group must be 0, 1 or 2, got %d", d.cta_group);
+    if (d.tile_m != 0 && d.tile_m != 128 && d.tile_m != 256)
+        return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "gemm_tn: tile_m must be 0, 128 or 256, got %d", d.tile_m);
     if (!c) return fail(CUTE_B200_ERR_NULL_POINTER, "gemm_tn: C is null");
     const bool c_bf16 = d.c_dtype == CUTE_B200_BF16;
     if (c & (c_bf16 ? 1u : 3u)) return fail(CUTE_B200_ERR_MISALIGNED, "gemm_tn: C is not aligned to its element size");
@@ -561,8 +657,8 @@ cute_b200_status gemm_tn(const cute_b200_gemm_desc &d, uint64_t a, uint64_t b, u
     if (!a || !b) return fail(CUTE_B200_ERR_NULL_POINTER, "gemm_tn: A or B is null");
     if ((a | b) & 15u) return fail(CUTE_B200_ERR_MISALIGNED, "gemm_tn: A and B must be 16-byte aligned");
 
-    const int bn = d.tile_n ? d.tile_n : (d.n > 128 ? 256 : 128);
-    const int group = d.cta_group ? d.cta_group : (d.m > BM ? 2 : 1);
+    int group = 2, bn = 256, mh = 2;
+    choose_tiling(d.m, d.n, dev.sm_count, d.cta_group, d.tile_n, d.tile_m / 128, &group, &bn, &mh);
 
     GemmParams p = {};
     p.C = reinterpret_cast<void *>(c);
@@ -573,30 +669,26 @@ cute_b200_status gemm_tn(const cute_b200_gemm_desc &d, uint64_t a, uint64_t b, u
     p.alpha = d.alpha;
     p.beta = d.beta;
     p.status = dev.status_word;
-    p.debug = d.reserved[0];
+    p.debug = d.tuning[0];
+    p.group_m = d.tuning[1];
+    p.stage_limit = d.tuning[2];
     const size_t c_elem = c_bf16 ? 2 : 4;
     p.c_vec_ok = ((c & 15u) == 0 && (size_t(d.n) * c_elem) % 16 == 0) ? 1 : 0;
+    if ((c & 31u) == 0 && (size_t(d.n) * c_elem) % 32 == 0) p.c_vec_ok = 2;
     const uint32_t fmt = d.ab_dtype == CUTE_B200_BF16 ? 1u : 0u;
     // Instruction descriptor: f32 accumulator, A and B format, both K-major,
     // N >> 3 at bit 17, M >> 4 at bit 24 (M counts the rows of the whole pair).
     p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(bn >> 3) << 17) | (uint32_t((BM * group) >> 4) << 24);
 
     CUtensorMap tmA, tmB;
-    CB_TRY(make_tensor_map(&tmA, a, d.ab_dtype, d.m, d.k, BM));
+    CB_TRY(make_tensor_map(&tmA, a, d.ab_dtype, d.m, d.k, BM * mh));
     CB_TRY(make_tensor_map(&tmB, b, d.ab_dtype, d.n, d.k, bn / group));
 
-#define CB_GEMM_CASE(G, N_, BF)                                                       \
-    if (group == G && bn == N_ && c_bf16 == BF) return launch<G, N_, BF>(tmA, tmB, p, dev.sm_count, stream);
-    CB_GEMM_CASE(1, 128, false)
-    CB_GEMM_CASE(1, 128, true)
-    CB_GEMM_CASE(1, 256, false)
-    CB_GEMM_CASE(1, 256, true)
-    CB_GEMM_CASE(2, 128, false)
-    CB_GEMM_CASE(2, 128, true)
-    CB_GEMM_CASE(2, 256, false)
-    CB_GEMM_CASE(2, 256, true)
-#undef CB_GEMM_CASE
-    return fail(CUTE_B200_ERR_UNSUPPORTED, "gemm_tn: no kernel for cta_group %d, tile_n %d", group, bn);
+#define CB_CASE(G, N_, H, BF) \
+    if (group == G && bn == N_ && mh == H && c_bf16 == BF) return launch<G, N_, H, BF>(tmA, tmB, p, dev.sm_count, stream);
+    CB_GEMM_VARIANTS(CB_CASE)
+#undef CB_CASE
+    return fail(CUTE_B200_ERR_UNSUPPORTED, "gemm_tn: no kernel for cta_group %d, tile %d x %d", group, BM * mh, bn);
 }
 
 }  // namespace cb

@@ -87,9 +87,11 @@ typedef struct {
     int32_t ab_dtype; /* CUTE_B200_F16 or CUTE_B200_BF16 */
     int32_t c_dtype;  /* CUTE_B200_F32 or CUTE_B200_BF16 */
     float alpha, beta;
-    int32_t tile_n;    /* 0 = choose; 128 or 256 */
-    int32_t cta_group; /* 0 = choose; 1 = one CTA per tile; 2 = CTA pair per 256-row tile */
-    int32_t reserved[4]; /* zero */
+    int32_t tile_n;    /* columns of C per tile: 0 = choose; 128 or 256 */
+    int32_t cta_group; /* 0 = choose; 1 = one CTA per tile; 2 = a CTA pair shares each tile's MMAs */
+    int32_t tile_m;    /* rows of C per CTA: 0 = choose; 128 or 256 */
+    int32_t tuning[3]; /* zero.  Measurement knobs: [0] bit 0 skips the loads, bit 1 the stores (results
+                          are then meaningless); [1] row tiles walked per column step; [2] ring stages used */
 } cute_b200_gemm_desc;
 
 cute_b200_status cute_b200_gemm_tn(const cute_b200_gemm_desc *desc, uint64_t dA, uint64_t dB, uint64_t dC,

@@ -25,7 +25,7 @@ def host(t, dtype):
     return a.view(np.uint16) if dtype == np.uint16 else a
 
 
-def run_gemm(lib, a_bits, b_bits, ab, cdt, alpha=1.0, beta=0.0, c0=None, tile_n=0, cta_group=0):
+def run_gemm(lib, a_bits, b_bits, ab, cdt, alpha=1.0, beta=0.0, c0=None, tile_n=0, cta_group=0, tile_m=0):
     import torch
     (m, k), n = a_bits.shape, b_bits.shape[0]
     if c0 is None:
@@ -33,7 +33,7 @@ def run_gemm(lib, a_bits, b_bits, ab, cdt, alpha=1.0, beta=0.0, c0=None, tile_n=
     dA, dB, dC = dev(a_bits), dev(b_bits), dev(c0)
     a_ptr = dA.data_ptr() if k else 0
     b_ptr = dB.data_ptr() if k else 0
-    lib.gemm_tn(lib.gemm_desc(m, n, k, ab, cdt, alpha, beta, tile_n, cta_group), a_ptr, b_ptr, dC.data_ptr(), 0)
+    lib.gemm_tn(lib.gemm_desc(m, n, k, ab, cdt, alpha, beta, tile_n, cta_group, tile_m), a_ptr, b_ptr, dC.data_ptr(), 0)
     torch.cuda.synchronize()
     assert lib.device_status() == (0, 0, 0, 0)
     return host(dC, c0.dtype).reshape(m, n)
@@ -179,12 +179,13 @@ GEMM_SHAPES = [(128, 128, 64), (256, 128, 96), (128, 256, 160), (256, 256, 256),
 
 @pytest.mark.parametrize("m,n,k", GEMM_SHAPES)
 @pytest.mark.parametrize("ab_name", ["f16", "bf16"])
-@pytest.mark.parametrize("cta_group,tile_n", [(1, 128), (1, 256), (2, 128), (2, 256), (0, 0)])
-def test_gemm_small_integers_bit_exact(lib, gpu, m, n, k, ab_name, cta_group, tile_n):
+@pytest.mark.parametrize("cta_group,tile_n,tile_m", [(1, 128, 128), (1, 256, 128), (2, 128, 128), (2, 256, 128), (1, 128, 256),
+                                                      (1, 256, 256), (2, 128, 256), (2, 256, 256), (0, 0, 0)])
+def test_gemm_small_integers_bit_exact(lib, gpu, m, n, k, ab_name, cta_group, tile_n, tile_m):
     ab = lib.F16 if ab_name == "f16" else lib.BF16
     a, b, _ = lcg_buffers([m * k, n * k, 0], small=True)
     a_bits, b_bits = conv(lib, ab)(a.reshape(m, k)), conv(lib, ab)(b.reshape(n, k))
-    got = run_gemm(lib, a_bits, b_bits, ab, lib.F32, tile_n=tile_n, cta_group=cta_group)
+    got = run_gemm(lib, a_bits, b_bits, ab, lib.F32, tile_n=tile_n, cta_group=cta_group, tile_m=tile_m)
     want = oracle.gemm_tn(a_bits, b_bits, ab)
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
 
@@ -202,12 +203,12 @@ def test_gemm_example_inputs_match_golden(lib, gpu, golden, shape, ab_name):
 
 @pytest.mark.parametrize("m,n,k", [(256, 128, 96), (256, 256, 256), (512, 384, 2048)])
 @pytest.mark.parametrize("ab_name", ["f16", "bf16"])
-@pytest.mark.parametrize("cta_group", [1, 2])
-def test_gemm_random_within_reference_bound(lib, gpu, m, n, k, ab_name, cta_group):
+@pytest.mark.parametrize("cta_group,tile_m", [(1, 128), (2, 128), (2, 256)])
+def test_gemm_random_within_reference_bound(lib, gpu, m, n, k, ab_name, cta_group, tile_m):
     ab = lib.F16 if ab_name == "f16" else lib.BF16
     a, b, _ = lcg_buffers([m * k, n * k, 0], small=False)
     a_bits, b_bits = conv(lib, ab)(a.reshape(m, k)), conv(lib, ab)(b.reshape(n, k))
-    got = run_gemm(lib, a_bits, b_bits, ab, lib.F32, cta_group=cta_group)
+    got = run_gemm(lib, a_bits, b_bits, ab, lib.F32, cta_group=cta_group, tile_m=tile_m)
     want = oracle.gemm_tn(a_bits, b_bits, ab)
     allowed = tensor_core_bound(k, oracle.gemm_tn_abs(a_bits, b_bits, ab))
     assert (np.abs(got.astype(np.float64) - want.astype(np.float64)) <= allowed).all()
@@ -225,12 +226,12 @@ def test_gemm_config0_256_cubed_uniform_seed0(lib, gpu):
 
 @pytest.mark.parametrize("m,n,k", [(1, 1, 8), (100, 200, 72), (200, 136, 8), (129, 257, 520), (300, 520, 200), (128, 130, 64)])
 @pytest.mark.parametrize("cdt_name", ["f32", "bf16"])
-@pytest.mark.parametrize("cta_group", [1, 2])
-def test_gemm_ragged_shapes(lib, gpu, m, n, k, cdt_name, cta_group):
+@pytest.mark.parametrize("cta_group,tile_m", [(1, 128), (2, 128), (2, 256), (1, 256)])
+def test_gemm_ragged_shapes(lib, gpu, m, n, k, cdt_name, cta_group, tile_m):
     cdt = lib.F32 if cdt_name == "f32" else lib.BF16
     a, b, _ = lcg_buffers([m * k, n * k, 0], small=True)
     a_bits, b_bits = oracle.f32_to_bf16_bits(a.reshape(m, k)), oracle.f32_to_bf16_bits(b.reshape(n, k))
-    got = run_gemm(lib, a_bits, b_bits, lib.BF16, cdt, cta_group=cta_group)
+    got = run_gemm(lib, a_bits, b_bits, lib.BF16, cdt, cta_group=cta_group, tile_m=tile_m)
     want = oracle.gemm_tn(a_bits, b_bits, lib.BF16, cdt)
     if cdt == lib.F32:
         assert np.array_equal(got, want)
@@ -240,13 +241,14 @@ def test_gemm_ragged_shapes(lib, gpu, m, n, k, cdt_name, cta_group):
 
 @pytest.mark.parametrize("cdt_name", ["f32", "bf16"])
 @pytest.mark.parametrize("alpha,beta", [(1.5, -0.5), (0.0, 1.0), (2.0, 0.0), (1.0, 1.0)])
-def test_gemm_alpha_beta_epilogue(lib, gpu, cdt_name, alpha, beta):
+@pytest.mark.parametrize("tile_m", [128, 256])
+def test_gemm_alpha_beta_epilogue(lib, gpu, cdt_name, alpha, beta, tile_m):
     cdt = lib.F32 if cdt_name == "f32" else lib.BF16
     m, n, k = 256, 384, 128
     a, b, c = lcg_buffers([m * k, n * k, m * n], small=True)
     a_bits, b_bits = oracle.f32_to_f16_bits(a.reshape(m, k)), oracle.f32_to_f16_bits(b.reshape(n, k))
     c0 = c.reshape(m, n) if cdt == lib.F32 else oracle.f32_to_bf16_bits(c.reshape(m, n))
-    got = run_gemm(lib, a_bits, b_bits, lib.F16, cdt, alpha, beta, c0=c0)
+    got = run_gemm(lib, a_bits, b_bits, lib.F16, cdt, alpha, beta, c0=c0, tile_m=tile_m)
     want = oracle.gemm_tn(a_bits, b_bits, lib.F16, cdt, alpha, beta, c_init=c0)
     assert np.array_equal(got, want)
 
@@ -320,7 +322,7 @@ def test_gemm_full_size_properties(lib, gpu):
     lib.gemm_tn(lib.gemm_desc(n, n, n, lib.BF16, lib.F32), A2.data_ptr(), B.data_ptr(), C2.data_ptr(), 0)
     torch.cuda.synchronize()
     assert torch.equal(C2, C1 * 2)  # scaling by two is exact at every step
-    lib.gemm_tn(lib.gemm_desc(n, n, n, lib.BF16, lib.F32, tile_n=128, cta_group=1), A.data_ptr(), B.data_ptr(), C2.data_ptr(), 0)
+    lib.gemm_tn(lib.gemm_desc(n, n, n, lib.BF16, lib.F32, tile_n=128, cta_group=1, tile_m=128), A.data_ptr(), B.data_ptr(), C2.data_ptr(), 0)
     torch.cuda.synchronize()
     assert torch.equal(C2, C1)  # same k order per output in every tiling
     a_bits = A[4000:4016].view(torch.int16).cpu().numpy().view(np.uint16)
