@@ -36,7 +36,7 @@ class GemmDesc(ctypes.Structure):
     _fields_ = [("m", ctypes.c_int32), ("n", ctypes.c_int32), ("k", ctypes.c_int32), ("ab_dtype", ctypes.c_int32),
                 ("c_dtype", ctypes.c_int32), ("alpha", ctypes.c_float), ("beta", ctypes.c_float),
                 ("tile_n", ctypes.c_int32), ("cta_group", ctypes.c_int32), ("tile_m", ctypes.c_int32),
-                ("tuning", ctypes.c_int32 * 3)]
+                ("split_k", ctypes.c_int32), ("tuning", ctypes.c_int32 * 2)]
 
 
 class Arg(ctypes.Structure):
@@ -115,8 +115,10 @@ def init(device: int = 0) -> None:
     check(load().cute_b200_init(device))
 
 
-def gemm_desc(m, n, k, ab_dtype, c_dtype, alpha=1.0, beta=0.0, tile_n=0, cta_group=0, tile_m=0) -> GemmDesc:
-    return GemmDesc(m, n, k, ab_dtype, c_dtype, alpha, beta, tile_n, cta_group, tile_m, (ctypes.c_int32 * 3)(0, 0, 0))
+def gemm_desc(m, n, k, ab_dtype, c_dtype, alpha=1.0, beta=0.0, tile_n=0, cta_group=0, tile_m=0,
+              split_k=0) -> GemmDesc:
+    return GemmDesc(m, n, k, ab_dtype, c_dtype, alpha, beta, tile_n, cta_group, tile_m, split_k,
+                    (ctypes.c_int32 * 2)(0, 0))
 
 
 def gemm_tn(desc: GemmDesc, dA: int, dB: int, dC: int, stream: int = 0) -> None:

@@ -373,6 +373,7 @@ cute_b200_status cute_b200_release_workspace(void) {
         cudaGetLastError();
         return CUTE_B200_OK;
     }
+    gemm_tn_release_scratch();
     Workspace &w = g_workspace[device];
     for (int i = 0; i < 3; i++) {
         if (w.ptr[i]) cudaFree(w.ptr[i]);

@@ -86,7 +86,8 @@ struct GemmParams {
     int m_tiles, n_tiles, group_m;
     int c_vec_ok;  // C base and row pitch allow 16-byte (1) or 32-byte (2) accesses
     int debug;     // timing experiments only: bit 0 skips the TMA loads, bit 1 skips the stores
-    int stage_limit;  // timing experiments only: use this many ring stages (0 = all)
+    int splits;              // k is cut into this many ranges, one work unit each (1 = no split)
+    size_t split_stride;     // bytes between the partial-sum planes of consecutive ranges
     uint32_t *status;
 };
 
@@ -142,16 +143,26 @@ __device__ __forceinline__ TileCoord tile_coord(int t, const GemmParams &p) {
     return {first + r % gm, r / gm};
 }
 
+// A work unit is one k range of one tile: unit u = tile * splits + range.
+struct Unit {
+    int tile, range, kb0, kb1;
+};
+__device__ __forceinline__ Unit unit_of(int u, const GemmParams &p, int k_blocks) {
+    const int range = u % p.splits, per = (k_blocks + p.splits - 1) / p.splits;
+    const int kb0 = min(range * per, k_blocks);
+    return {u / p.splits, range, kb0, min(kb0 + per, k_blocks)};
+}
+
 template <bool C_BF16>
-__device__ __forceinline__ void store_chunk(const GemmParams &p, int row, int col0, const uint32_t (&v)[32],
-                                            bool plain) {
+__device__ __forceinline__ void store_chunk(const GemmParams &p, void *cbase, int row, int col0,
+                                            const uint32_t (&v)[32], bool plain) {
     if (row >= p.M || col0 >= p.N) return;
     const float alpha = p.alpha, beta = p.beta;
     auto epi = [&](uint32_t acc_bits, float c_old) {
         return __fadd_rn(__fmul_rn(alpha, __uint_as_float(acc_bits)), __fmul_rn(beta, c_old));
     };
     if constexpr (!C_BF16) {
-        float *crow = reinterpret_cast<float *>(p.C) + size_t(row) * p.ldc + col0;
+        float *crow = reinterpret_cast<float *>(cbase) + size_t(row) * p.ldc + col0;
         if (p.c_vec_ok == 2 && plain && col0 + 32 <= p.N) {
 #pragma unroll
             for (int g = 0; g < 4; g++)
@@ -177,7 +188,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams &p, int row, int co
                 if (col0 + j < p.N) crow[j] = plain ? __uint_as_float(v[j]) : epi(v[j], crow[j]);
         }
     } else {
-        __nv_bfloat16 *crow = reinterpret_cast<__nv_bfloat16 *>(p.C) + size_t(row) * p.ldc + col0;
+        __nv_bfloat16 *crow = reinterpret_cast<__nv_bfloat16 *>(cbase) + size_t(row) * p.ldc + col0;
         if (p.c_vec_ok == 2 && plain && col0 + 32 <= p.N) {
             uint32_t w[16];
 #pragma unroll
@@ -244,9 +255,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     const uint32_t rank = CTA_GROUP == 1 ? 0u : ptx::cluster_ctarank();
     const int cluster_id = blockIdx.x / CTA_GROUP;
     const int num_clusters = gridDim.x / CTA_GROUP;
-    const int num_tiles = p.m_tiles * p.n_tiles;
+    const int num_units = p.m_tiles * p.n_tiles * p.splits;
     const int k_blocks = (p.K + BK - 1) / BK;
-    const int nstages = (p.stage_limit > 0 && p.stage_limit < C::STAGES) ? p.stage_limit : C::STAGES;
+    constexpr int nstages = C::STAGES;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; s++) {
@@ -284,11 +295,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             uint32_t ph = 0;
             uint32_t filled = 0, filled_parity = 0;  // per stage: was it filled, and in which phase
             bool ok = true;
-            for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
-                const TileCoord tc = tile_coord(t, p);
+            for (int t = cluster_id; t < num_units && ok; t += num_clusters) {
+                const Unit u = unit_of(t, p, k_blocks);
+                const TileCoord tc = tile_coord(u.tile, p);
                 const int row_a = (tc.tm * CTA_GROUP + int(rank)) * C::A_ROWS;
                 const int row_b = tc.tn * BN + int(rank) * C::B_ROWS;
-                for (int kb = 0; kb < k_blocks; kb++) {
+                for (int kb = u.kb0; kb < u.kb1; kb++) {
                     if (!wait_bar(empty_bar(s), ph ^ 1u, abort_flag, p.status, WHERE_PRODUCER, uint32_t(s))) {
                         ok = false;
                         break;
@@ -331,16 +343,19 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         __syncwarp();
     } else if (warp == 1) {
         // ---------------------------------------------------------- MMA issuer
-        if (lane == 0 && rank == 0 && k_blocks > 0) {
+        if (lane == 0 && rank == 0) {
             int s = 0;
             uint32_t ph = 0;
             bool ok = true, issued = false;
             int it = 0;
-            for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, it++) {
+            for (int t = cluster_id; t < num_units && ok; t += num_clusters) {
+                const Unit u = unit_of(t, p, k_blocks);
+                if (u.kb0 >= u.kb1) continue;  // an empty k range uses no accumulator
                 const int buf = it % C::ACC_BUFS;
                 const uint32_t aph = uint32_t(it / C::ACC_BUFS) & 1u;
+                it++;
                 const uint32_t d_tmem = tmem_base + uint32_t(buf * C::ACC_COLS);
-                for (int kb = 0; kb < k_blocks && ok; kb++) {
+                for (int kb = u.kb0; kb < u.kb1 && ok; kb++) {
                     if (!wait_bar(full_bar(s), ph, abort_flag, p.status, WHERE_MMA_FULL, uint32_t(s))) {
                         ok = false;
                         break;
@@ -350,7 +365,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                     const uint64_t b_desc = sw128_desc(a_src + C::A_BYTES);
 #pragma unroll
                     for (int h = 0; h < MH; h++) {
-                        if (kb == 0) {
+                        if (kb == u.kb0) {
                             // The epilogue must have drained this half of the buffer
                             // (a fresh barrier passes at once).
                             if (!wait_bar(tempty_bar(buf, h), aph ^ 1u, abort_flag, p.status, WHERE_MMA_TMEM,
@@ -365,7 +380,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                         for (int j = 0; j < BK / UMMA_K; j++) {
                             // 16 elements of k = 32 bytes = 2 units of the address field
                             ptx::umma_f16<CTA_GROUP>(d_tmem + uint32_t(h * BN), a_desc + 2u * j, b_desc + 2u * j, p.idesc,
-                                                     (kb > 0 || j > 0) ? 1u : 0u);
+                                                     (kb > u.kb0 || j > 0) ? 1u : 0u);
                         }
                         issued = true;
                     }
@@ -402,12 +417,15 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         const bool plain = (p.alpha == 1.0f && p.beta == 0.0f);
         bool ok = true;
         int it = 0;
-        for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, it++) {
-            const TileCoord tc = tile_coord(t, p);
+        for (int t = cluster_id; t < num_units && ok; t += num_clusters) {
+            const Unit u = unit_of(t, p, k_blocks);
+            const TileCoord tc = tile_coord(u.tile, p);
+            const bool have_acc = u.kb0 < u.kb1;  // else this range contributes zeros
             const int buf = it % C::ACC_BUFS;
             const uint32_t aph = uint32_t(it / C::ACC_BUFS) & 1u;
-            const bool have_acc = k_blocks > 0;
+            void *cbase = reinterpret_cast<uint8_t *>(p.C) + size_t(u.range) * p.split_stride;
             if (have_acc) {
+                it++;
                 if (!wait_bar(tfull_bar(buf), aph, abort_flag, p.status, WHERE_EPILOGUE, uint32_t(buf))) {
                     ok = false;
                     break;
@@ -436,7 +454,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                         else ptx::mbar_arrive_cluster(ptx::mapa(tempty_bar(buf, i / CH), 0));
                     }
                 }
-                if (!(p.debug & 2)) store_chunk<C_BF16>(p, row0 + (i / CH) * BM, tc.tn * BN + col_of(i), v, plain);
+                if (!(p.debug & 2)) store_chunk<C_BF16>(p, cbase, row0 + (i / CH) * BM, tc.tn * BN + col_of(i), v, plain);
             };
             // Two register buffers: the TMEM read of the next chunk is in flight
             // while the current one is converted and stored.
@@ -477,6 +495,45 @@ __global__ void gemm_k0_kernel(void *C, size_t count, float alpha, float beta) {
     } else {
         float *c = reinterpret_cast<float *>(C);
         c[i] = plain ? 0.0f : __fadd_rn(__fmul_rn(alpha, 0.0f), __fmul_rn(beta, c[i]));
+    }
+}
+
+// Second pass of a split-k GEMM: C = alpha * (P_0 + P_1 + ... ) + beta * C over
+// the f32 partial planes, ranges added in ascending order.
+template <bool C_BF16>
+__global__ void __launch_bounds__(256) gemm_splitk_reduce(const float *__restrict__ partial, int splits, size_t plane,
+                                                          size_t count, void *C, float alpha, float beta) {
+    const size_t i4 = (size_t(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
+    if (i4 >= count) return;
+    const bool plain = (alpha == 1.0f && beta == 0.0f);
+    float acc[4];
+    const int n = int(min(size_t(4), count - i4));
+    if (n == 4) {
+        float4 a = *reinterpret_cast<const float4 *>(partial + i4);
+        for (int s = 1; s < splits; s++) {
+            const float4 b = *reinterpret_cast<const float4 *>(partial + s * plane + i4);
+            a.x = __fadd_rn(a.x, b.x);
+            a.y = __fadd_rn(a.y, b.y);
+            a.z = __fadd_rn(a.z, b.z);
+            a.w = __fadd_rn(a.w, b.w);
+        }
+        acc[0] = a.x, acc[1] = a.y, acc[2] = a.z, acc[3] = a.w;
+    } else {
+        for (int j = 0; j < n; j++) {
+            float a = partial[i4 + j];
+            for (int s = 1; s < splits; s++) a = __fadd_rn(a, partial[s * plane + i4 + j]);
+            acc[j] = a;
+        }
+    }
+    for (int j = 0; j < n; j++) {
+        if constexpr (C_BF16) {
+            __nv_bfloat16 *c = reinterpret_cast<__nv_bfloat16 *>(C) + i4 + j;
+            const float r = plain ? acc[j] : __fadd_rn(__fmul_rn(alpha, acc[j]), __fmul_rn(beta, __bfloat162float(*c)));
+            *c = __float2bfloat16_rn(r);
+        } else {
+            float *c = reinterpret_cast<float *>(C) + i4 + j;
+            *c = plain ? acc[j] : __fadd_rn(__fmul_rn(alpha, acc[j]), __fmul_rn(beta, *c));
+        }
     }
 }
 
@@ -543,7 +600,7 @@ cute_b200_status launch(const CUtensorMap &tmA, const CUtensorMap &tmB, GemmPara
     const int tile_rows = BM * MH * CTA_GROUP;
     p.m_tiles = (p.M + tile_rows - 1) / tile_rows;
     p.n_tiles = (p.N + BN - 1) / BN;
-    const long long tiles = (long long)p.m_tiles * p.n_tiles;
+    const long long tiles = (long long)p.m_tiles * p.n_tiles * p.splits;
     int clusters = sm_count / CTA_GROUP;
     if (tiles < clusters) clusters = int(tiles);
     // Walk about sqrt(#concurrent tiles) row tiles before moving to the next
@@ -595,29 +652,75 @@ double tiling_efficiency(int group, int bn, int mh) {
     return e;
 }
 
-// Pick the tiling with the smallest estimated time: whole waves of tiles over
-// the clusters that fit, divided by the tiling's efficiency.
-void choose_tiling(int m, int n, int sm_count, int want_group, int want_bn, int want_mh, int *group, int *bn, int *mh) {
+// Pick tiling and k split with the smallest estimated time.  A launch runs
+// whole waves of work units (tile x k range) over the clusters that fit; a
+// unit costs its MMA time plus a fixed start/drain latency; a split GEMM also
+// pays a second pass over the f32 partial planes.
+void choose_tiling(int m, int n, int k, int c_bytes, int sm_count, int want_group, int want_bn, int want_mh,
+                   int want_splits, int *group, int *bn, int *mh, int *splits) {
+    const double sm_rate = 1.0e13;       // dense 16-bit flop/s of one SM at the clocks a GEMM sustains
+    const double unit_latency = 2.5e-6;  // fill the ring, drain the accumulator
+    const double hbm = 5.0e12;
+    const int k_blocks = (k + BK - 1) / BK;
     double best = 1e300;
     for (int g = 1; g <= 2; g++)
         for (int b = 128; b <= 256; b += 128)
-            for (int h = 1; h <= 2; h++) {
-                if ((want_group && g != want_group) || (want_bn && b != want_bn) || (want_mh && h != want_mh)) continue;
-                const long long rows = 128LL * g * h;
-                const long long tiles = ((m + rows - 1) / rows) * ((n + b - 1) / b);
-                const long long clusters = sm_count / g;
-                const long long waves = (tiles + clusters - 1) / clusters;
-                const double t = double(waves) * double(rows) * b / (g * tiling_efficiency(g, b, h));
-                if (t < best) {
-                    best = t;
-                    *group = g;
-                    *bn = b;
-                    *mh = h;
+            for (int h = 1; h <= 2; h++)
+                for (int s = 1; s <= 16; s++) {
+                    if ((want_group && g != want_group) || (want_bn && b != want_bn) || (want_mh && h != want_mh) ||
+                        (want_splits && s != want_splits))
+                        continue;
+                    if (s > 1 && (s > k_blocks / 4 || double(s) * m * n * 4 > 512e6)) continue;
+                    const long long rows = 128LL * g * h;
+                    const long long units = ((m + rows - 1) / rows) * ((n + b - 1) / b) * s;
+                    const long long clusters = sm_count / g;
+                    const long long waves = (units + clusters - 1) / clusters;
+                    const int kb_per = (k_blocks + s - 1) / s;
+                    const double unit_time =
+                        2.0 * rows * b * kb_per * BK / (g * sm_rate * tiling_efficiency(g, b, h)) + unit_latency;
+                    double t = waves * unit_time;
+                    if (s > 1) t += (double(s + 1) * m * n * 4 + double(m) * n * c_bytes) / hbm + 3e-6;
+                    if (t < best) {
+                        best = t;
+                        *group = g, *bn = b, *mh = h, *splits = s;
+                    }
                 }
-            }
+}
+
+// Grow-only scratch of the split-k path, one per device.
+void *g_scratch_ptr[64] = {};
+size_t g_scratch_size[64] = {};
+std::mutex g_scratch_mu;
+
+cute_b200_status scratch_get(size_t bytes, void **out) {
+    void **ptr = g_scratch_ptr;
+    size_t *size = g_scratch_size;
+    std::mutex &mu = g_scratch_mu;
+    int device = 0;
+    CB_CUDA(cudaGetDevice(&device));
+    if (device < 0 || device >= 64) return fail(CUTE_B200_ERR_NO_DEVICE, "no current device");
+    std::lock_guard<std::mutex> lock(mu);
+    if (size[device] < bytes) {
+        if (ptr[device]) CB_CUDA(cudaFree(ptr[device]));
+        ptr[device] = nullptr;
+        size[device] = 0;
+        CB_CUDA(cudaMalloc(&ptr[device], bytes));
+        size[device] = bytes;
+    }
+    *out = ptr[device];
+    return CUTE_B200_OK;
 }
 
 }  // namespace
+
+void gemm_tn_release_scratch() {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return;
+    std::lock_guard<std::mutex> lock(g_scratch_mu);
+    if (g_scratch_ptr[device]) cudaFree(g_scratch_ptr[device]);
+    g_scratch_ptr[device] = nullptr;
+    g_scratch_size[device] = 0;
+}
 
 cute_b200_status gemm_tn_init(const DeviceState &) {
 #define CB_SET(G, N_, H, BF) CB_TRY((set_smem_limit<G, N_, H, BF>()));
@@ -657,8 +760,13 @@ cute_b200_status gemm_tn(const cute_b200_gemm_desc &d, uint64_t a, uint64_t b, u
     if (!a || !b) return fail(CUTE_B200_ERR_NULL_POINTER, "gemm_tn: A or B is null");
     if ((a | b) & 15u) return fail(CUTE_B200_ERR_MISALIGNED, "gemm_tn: A and B must be 16-byte aligned");
 
-    int group = 2, bn = 256, mh = 2;
-    choose_tiling(d.m, d.n, dev.sm_count, d.cta_group, d.tile_n, d.tile_m / 128, &group, &bn, &mh);
+    if (d.split_k < 0 || d.split_k > 16)
+        return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "gemm_tn: split_k must be 0 (choose) to 16, got %d", d.split_k);
+    int group = 2, bn = 256, mh = 2, splits = 1;
+    choose_tiling(d.m, d.n, d.k, c_bf16 ? 2 : 4, dev.sm_count, d.cta_group, d.tile_n, d.tile_m / 128, d.split_k, &group,
+                  &bn, &mh, &splits);
+    const int max_splits = ((d.k + BK - 1) / BK);
+    if (splits > max_splits) splits = max_splits;
 
     GemmParams p = {};
     p.C = reinterpret_cast<void *>(c);
@@ -671,7 +779,8 @@ cute_b200_status gemm_tn(const cute_b200_gemm_desc &d, uint64_t a, uint64_t b, u
     p.status = dev.status_word;
     p.debug = d.tuning[0];
     p.group_m = d.tuning[1];
-    p.stage_limit = d.tuning[2];
+    p.splits = splits;
+    p.split_stride = 0;
     const size_t c_elem = c_bf16 ? 2 : 4;
     p.c_vec_ok = ((c & 15u) == 0 && (size_t(d.n) * c_elem) % 16 == 0) ? 1 : 0;
     if ((c & 31u) == 0 && (size_t(d.n) * c_elem) % 32 == 0) p.c_vec_ok = 2;
@@ -684,6 +793,36 @@ cute_b200_status gemm_tn(const cute_b200_gemm_desc &d, uint64_t a, uint64_t b, u
     CB_TRY(make_tensor_map(&tmA, a, d.ab_dtype, d.m, d.k, BM * mh));
     CB_TRY(make_tensor_map(&tmB, b, d.ab_dtype, d.n, d.k, bn / group));
 
+    if (splits > 1) {
+        // First pass: every k range writes an f32 plane of partial sums into the
+        // library's scratch buffer; second pass adds the planes and applies the
+        // epilogue.  The scratch is allocated on first need and kept.
+        const size_t plane = size_t(d.m) * d.n;
+        void *scratch = nullptr;
+        CB_TRY(scratch_get(plane * 4 * splits, &scratch));
+        GemmParams q = p;
+        q.C = scratch;
+        q.alpha = 1.0f;
+        q.beta = 0.0f;
+        q.split_stride = plane * 4;
+        q.c_vec_ok = (size_t(d.n) * 4) % 32 == 0 ? 2 : ((size_t(d.n) * 4) % 16 == 0 ? 1 : 0);
+        cute_b200_status st = CUTE_B200_ERR_UNSUPPORTED;
+#define CB_CASE(G, N_, H, BF) \
+    if (group == G && bn == N_ && mh == H && !BF) st = launch<G, N_, H, false>(tmA, tmB, q, dev.sm_count, stream);
+        CB_GEMM_VARIANTS(CB_CASE)
+#undef CB_CASE
+        CB_TRY(st);
+        const unsigned blocks = unsigned((plane + 1023) / 1024);
+        if (c_bf16)
+            gemm_splitk_reduce<true><<<blocks, 256, 0, stream>>>(static_cast<const float *>(scratch), splits, plane, plane,
+                                                                 p.C, d.alpha, d.beta);
+        else
+            gemm_splitk_reduce<false><<<blocks, 256, 0, stream>>>(static_cast<const float *>(scratch), splits, plane, plane,
+                                                                  p.C, d.alpha, d.beta);
+        CB_CUDA(cudaGetLastError());
+        count_launch();
+        return CUTE_B200_OK;
+    }
 #define CB_CASE(G, N_, H, BF) \
     if (group == G && bn == N_ && mh == H && c_bf16 == BF) return launch<G, N_, H, BF>(tmA, tmB, p, dev.sm_count, stream);
     CB_GEMM_VARIANTS(CB_CASE)

@@ -90,8 +90,10 @@ typedef struct {
     int32_t tile_n;    /* columns of C per tile: 0 = choose; 128 or 256 */
     int32_t cta_group; /* 0 = choose; 1 = one CTA per tile; 2 = a CTA pair shares each tile's MMAs */
     int32_t tile_m;    /* rows of C per CTA: 0 = choose; 128 or 256 */
-    int32_t tuning[3]; /* zero.  Measurement knobs: [0] bit 0 skips the loads, bit 1 the stores (results
-                          are then meaningless); [1] row tiles walked per column step; [2] ring stages used */
+    int32_t split_k;   /* k ranges computed as separate work units and summed by a second kernel through an
+                          f32 scratch buffer the library allocates on first need: 0 = choose, 1 = never, <= 16 */
+    int32_t tuning[2]; /* zero.  Measurement knobs: [0] bit 0 skips the loads, bit 1 the stores (results are
+                          then meaningless); [1] row tiles walked per column step */
 } cute_b200_gemm_desc;
 
 cute_b200_status cute_b200_gemm_tn(const cute_b200_gemm_desc *desc, uint64_t dA, uint64_t dB, uint64_t dC,

@@ -25,7 +25,7 @@ def host(t, dtype):
     return a.view(np.uint16) if dtype == np.uint16 else a
 
 
-def run_gemm(lib, a_bits, b_bits, ab, cdt, alpha=1.0, beta=0.0, c0=None, tile_n=0, cta_group=0, tile_m=0):
+def run_gemm(lib, a_bits, b_bits, ab, cdt, alpha=1.0, beta=0.0, c0=None, tile_n=0, cta_group=0, tile_m=0, split_k=0):
     import torch
     (m, k), n = a_bits.shape, b_bits.shape[0]
     if c0 is None:
@@ -33,7 +33,7 @@ def run_gemm(lib, a_bits, b_bits, ab, cdt, alpha=1.0, beta=0.0, c0=None, tile_n=
     dA, dB, dC = dev(a_bits), dev(b_bits), dev(c0)
     a_ptr = dA.data_ptr() if k else 0
     b_ptr = dB.data_ptr() if k else 0
-    lib.gemm_tn(lib.gemm_desc(m, n, k, ab, cdt, alpha, beta, tile_n, cta_group, tile_m), a_ptr, b_ptr, dC.data_ptr(), 0)
+    lib.gemm_tn(lib.gemm_desc(m, n, k, ab, cdt, alpha, beta, tile_n, cta_group, tile_m, split_k), a_ptr, b_ptr, dC.data_ptr(), 0)
     torch.cuda.synchronize()
     assert lib.device_status() == (0, 0, 0, 0)
     return host(dC, c0.dtype).reshape(m, n)
@@ -251,6 +251,32 @@ def test_gemm_alpha_beta_epilogue(lib, gpu, cdt_name, alpha, beta, tile_m):
     got = run_gemm(lib, a_bits, b_bits, lib.F16, cdt, alpha, beta, c0=c0, tile_m=tile_m)
     want = oracle.gemm_tn(a_bits, b_bits, lib.F16, cdt, alpha, beta, c_init=c0)
     assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 128, 512), (200, 136, 328), (512, 256, 1088), (128, 128, 64)])
+@pytest.mark.parametrize("split_k", [2, 3, 5, 16])
+@pytest.mark.parametrize("cdt_name,alpha,beta", [("f32", 1.0, 0.0), ("bf16", 1.0, 0.0), ("f32", 1.5, -0.5), ("bf16", 2.0, 1.0)])
+def test_gemm_split_k(lib, gpu, m, n, k, split_k, cdt_name, alpha, beta):
+    """k cut into ranges summed by the second kernel: exact on integer data,
+    including more ranges than k blocks (empty ranges contribute zeros)."""
+    cdt = lib.F32 if cdt_name == "f32" else lib.BF16
+    a, b, c = lcg_buffers([m * k, n * k, m * n], small=True)
+    a_bits, b_bits = oracle.f32_to_f16_bits(a.reshape(m, k)), oracle.f32_to_f16_bits(b.reshape(n, k))
+    c0 = c.reshape(m, n) if cdt == lib.F32 else oracle.f32_to_bf16_bits(c.reshape(m, n))
+    got = run_gemm(lib, a_bits, b_bits, lib.F16, cdt, alpha, beta, c0=c0, split_k=split_k)
+    want = oracle.gemm_tn(a_bits, b_bits, lib.F16, cdt, alpha, beta, c_init=c0)
+    assert np.array_equal(got, want)
+
+
+def test_gemm_split_k_random_within_bound(lib, gpu):
+    m, n, k = 256, 128, 4096
+    a, b, _ = lcg_buffers([m * k, n * k, 0], small=False)
+    a_bits, b_bits = oracle.f32_to_bf16_bits(a.reshape(m, k)), oracle.f32_to_bf16_bits(b.reshape(n, k))
+    want = oracle.gemm_tn(a_bits, b_bits, lib.BF16)
+    allowed = tensor_core_bound(k, oracle.gemm_tn_abs(a_bits, b_bits, lib.BF16))
+    for split_k in (0, 4, 8):  # 0: the library splits this shape on its own
+        got = run_gemm(lib, a_bits, b_bits, lib.BF16, lib.F32, split_k=split_k)
+        assert (np.abs(got.astype(np.float64) - want) <= allowed).all()
 
 
 def test_gemm_k_zero_and_write_only_c(lib, gpu):
