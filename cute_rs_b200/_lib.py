@@ -25,7 +25,7 @@ F16, BF16, F32, I32 = 0, 1, 2, 3
 
 EXPORTS = (
     "cute_b200_status_string", "cute_b200_last_error", "cute_b200_init", "cute_b200_gemm_tn", "cute_b200_sgemm_nt",
-    "cute_b200_gemm_tn_host", "cute_b200_release_workspace",
+    "cute_b200_gemm_tn_host", "cute_b200_release_workspace", "cute_b200_gemm_tn_static",
     "cute_b200_elementwise_add_f32", "cute_b200_launch", "cute_b200_launch_host", "cute_b200_upload",
     "cute_b200_download", "cute_b200_free", "cute_b200_synchronize", "cute_b200_shard_rows",
     "cute_b200_gemm_tn_shard", "cute_b200_device_status", "cute_b200_launch_count",
@@ -75,6 +75,7 @@ def load() -> ctypes.CDLL:
     L.cute_b200_last_error.restype = cp
     L.cute_b200_init.argtypes = [i32]
     L.cute_b200_gemm_tn.argtypes = [ctypes.POINTER(GemmDesc), u64, u64, u64, vp]
+    L.cute_b200_gemm_tn_static.argtypes = [ctypes.POINTER(GemmDesc), u64, u64, u64, vp]
     L.cute_b200_gemm_tn_host.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, vp, ctypes.POINTER(ctypes.c_double)]
     L.cute_b200_release_workspace.argtypes = []
     L.cute_b200_sgemm_nt.argtypes = [i32, i32, i32, f32, f32, u64, u64, u64, vp]
@@ -123,6 +124,11 @@ def gemm_desc(m, n, k, ab_dtype, c_dtype, alpha=1.0, beta=0.0, tile_n=0, cta_gro
 
 def gemm_tn(desc: GemmDesc, dA: int, dB: int, dC: int, stream: int = 0) -> None:
     check(load().cute_b200_gemm_tn(ctypes.byref(desc), dA, dB, dC, stream))
+
+
+def gemm_tn_static(desc: GemmDesc, dA: int, dB: int, dC: int, stream: int = 0) -> None:
+    """Split-k GEMM on the library's built-in scratch array: allocates nothing."""
+    check(load().cute_b200_gemm_tn_static(ctypes.byref(desc), dA, dB, dC, stream))
 
 
 def gemm_tn_host(desc: GemmDesc, hA: int, hB: int, hC: int) -> float:

@@ -427,6 +427,19 @@ cute_b200_status cute_b200_gemm_tn_host(const cute_b200_gemm_desc *desc, const v
     return st;
 }
 
+cute_b200_status cute_b200_gemm_tn_static(const cute_b200_gemm_desc *desc, uint64_t dA, uint64_t dB, uint64_t dC,
+                                          void *stream) {
+    if (!desc) return fail(CUTE_B200_ERR_NULL_POINTER, "gemm_tn_static: desc is null");
+    // A device already set up through cute_b200_init shares its status word, so
+    // a bounded-wait report shows up in cute_b200_synchronize as usual; otherwise
+    // the entry point uses status words of its own.  Nothing is initialised here.
+    int device = 0;
+    uint32_t *shared = nullptr;
+    if (cudaGetDevice(&device) == cudaSuccess && device >= 0 && device < kMaxDevices && g_devices[device].ready)
+        shared = g_devices[device].status_word;
+    return gemm_tn_static(*desc, dA, dB, dC, static_cast<cudaStream_t>(stream), shared);
+}
+
 cute_b200_status cute_b200_sgemm_nt(int32_t m, int32_t n, int32_t k, float alpha, float beta, uint64_t dA, uint64_t dB,
                                     uint64_t dC, void *stream) {
     DeviceState *dev;

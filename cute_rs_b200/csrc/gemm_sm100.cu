@@ -713,6 +713,151 @@ cute_b200_status scratch_get(size_t bytes, void **out) {
 
 }  // namespace
 
+// ---- split-k GEMM without any allocation -------------------------------------
+// Scratch and status words of cute_b200_gemm_tn_static: part of the library
+// image, so every GPU that loads the library holds them until the process ends.
+constexpr size_t kStaticScratchBytes = size_t(32) << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+static __device__ __align__(16) uint32_t g_static_status[4];
+
+namespace {
+struct StaticSetup {
+    bool ready = false;
+    void *scratch = nullptr;      // device address of g_static_scratch on this device
+    uint32_t *status = nullptr;   // device address of g_static_status on this device
+    int sm_count = 0;
+};
+StaticSetup g_static_setup[64];
+std::mutex g_static_mu;
+
+// Once per device, with that device current: resolve the device addresses of
+// the two arrays (their names are host-side stand-ins, not device pointers)
+// and raise the kernels' shared-memory limit.  Allocates nothing.
+cute_b200_status static_setup(int device, StaticSetup **out) {
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    StaticSetup &st = g_static_setup[device];
+    if (!st.ready) {
+        int major = 0;
+        CB_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device));
+        if (major != 10)
+            return fail(CUTE_B200_ERR_NO_DEVICE, "device %d is not sm_100; this library is built for sm_100a only", device);
+        CB_CUDA(cudaDeviceGetAttribute(&st.sm_count, cudaDevAttrMultiProcessorCount, device));
+        void *p = nullptr;
+        CB_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+        st.scratch = p;
+        CB_CUDA(cudaGetSymbolAddress(&p, g_static_status));
+        st.status = static_cast<uint32_t *>(p);
+#define CB_SET(G, N_, H, BF) CB_TRY((set_smem_limit<G, N_, H, BF>()));
+        CB_GEMM_VARIANTS(CB_SET)
+#undef CB_SET
+        st.ready = true;
+    }
+    *out = &st;
+    return CUTE_B200_OK;
+}
+}  // namespace
+
+cute_b200_status gemm_tn_static(const cute_b200_gemm_desc &d, uint64_t a, uint64_t b, uint64_t c, cudaStream_t stream,
+                                uint32_t *shared_status) {
+    if (d.m <= 0 || d.n <= 0 || d.k <= 0)
+        return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "gemm_tn_static: invalid size %dx%dx%d (k must be positive)", d.m,
+                    d.n, d.k);
+    if ((d.ab_dtype != CUTE_B200_F16 && d.ab_dtype != CUTE_B200_BF16) ||
+        (d.c_dtype != CUTE_B200_F32 && d.c_dtype != CUTE_B200_BF16))
+        return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "gemm_tn_static: f16/bf16 inputs and f32/bf16 output only");
+    if (d.k % 8) return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "gemm_tn_static: k must be a multiple of 8, got %d", d.k);
+    if ((d.tile_n != 0 && d.tile_n != 128 && d.tile_n != 256) || d.cta_group < 0 || d.cta_group > 2 ||
+        (d.tile_m != 0 && d.tile_m != 128 && d.tile_m != 256))
+        return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "gemm_tn_static: invalid tile_n, tile_m or cta_group");
+    if (d.split_k == 1 || d.split_k < 0 || d.split_k > 16)
+        return fail(CUTE_B200_ERR_INVALID_ARGUMENT,
+                    "gemm_tn_static is the split-k GEMM: split_k must be 0 (choose) or 2..16, got %d", d.split_k);
+    if (!a || !b || !c) return fail(CUTE_B200_ERR_NULL_POINTER, "gemm_tn_static: null buffer");
+    const bool c_bf16 = d.c_dtype == CUTE_B200_BF16;
+    if ((a | b) & 15u) return fail(CUTE_B200_ERR_MISALIGNED, "gemm_tn_static: A and B must be 16-byte aligned");
+    if (c & (c_bf16 ? 1u : 3u)) return fail(CUTE_B200_ERR_MISALIGNED, "gemm_tn_static: C is not aligned to its element size");
+    const int k_blocks = (d.k + BK - 1) / BK;
+    if (k_blocks < 2) return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "gemm_tn_static: k = %d is too short to split", d.k);
+
+    int device = 0;
+    CB_CUDA(cudaGetDevice(&device));
+    if (device < 0 || device >= 64) return fail(CUTE_B200_ERR_NO_DEVICE, "no current device");
+    StaticSetup *setup = nullptr;
+    CB_TRY(static_setup(device, &setup));
+
+    const size_t plane = size_t(d.m) * d.n;
+    const size_t max_splits_by_scratch = kStaticScratchBytes / (plane * 4);
+    if (max_splits_by_scratch < 2 || (d.split_k && size_t(d.split_k) > max_splits_by_scratch))
+        return fail(CUTE_B200_ERR_INVALID_ARGUMENT,
+                    "gemm_tn_static: %d x %d with %d k ranges needs %zu bytes of scratch, the built-in buffer holds %zu",
+                    d.m, d.n, d.split_k ? d.split_k : 2, plane * 4 * size_t(d.split_k ? d.split_k : 2), kStaticScratchBytes);
+
+    // Tiling as the allocating path would pick it, with the split limited to what
+    // the built-in buffer and k allow.
+    int group = 2, bn = 256, mh = 2, splits = 2;
+    {
+        double best = 1e300;
+        for (int s = 2; s <= 16; s++) {
+            if (d.split_k && s != d.split_k) continue;
+            if (size_t(s) > max_splits_by_scratch || s > k_blocks) continue;
+            int g2 = 0, b2 = 0, h2 = 0, s2 = 0;
+            choose_tiling(d.m, d.n, d.k, c_bf16 ? 2 : 4, setup->sm_count, d.cta_group, d.tile_n, d.tile_m / 128, s, &g2, &b2,
+                          &h2, &s2);
+            if (s2 != s) continue;  // this split is not admissible for the shape
+            const long long rows = 128LL * g2 * h2;
+            const long long units = ((d.m + rows - 1) / rows) * ((d.n + b2 - 1) / b2) * s;
+            const long long clusters = setup->sm_count / g2;
+            const double t = double((units + clusters - 1) / clusters) *
+                                 (2.0 * rows * b2 * ((k_blocks + s - 1) / s) * BK / (g2 * 1.0e13 * tiling_efficiency(g2, b2, h2)) + 2.5e-6) +
+                             double(s + 1) * plane * 4 / 5.0e12;
+            if (t < best) best = t, group = g2, bn = b2, mh = h2, splits = s;
+        }
+        if (best == 1e300) {
+            // The cost model admits no split (k too short for it): take the caller's or the smallest.
+            splits = d.split_k ? d.split_k : 2;
+            if (splits > k_blocks) splits = k_blocks;
+            int s2 = 1;
+            choose_tiling(d.m, d.n, d.k, c_bf16 ? 2 : 4, setup->sm_count, d.cta_group, d.tile_n, d.tile_m / 128, 1, &group, &bn,
+                          &mh, &s2);
+        }
+    }
+
+    GemmParams p = {};
+    p.C = setup->scratch;
+    p.M = d.m;
+    p.N = d.n;
+    p.K = d.k;
+    p.ldc = d.n;
+    p.alpha = 1.0f;
+    p.beta = 0.0f;
+    p.status = shared_status ? shared_status : setup->status;
+    p.splits = splits;
+    p.split_stride = plane * 4;
+    p.c_vec_ok = (size_t(d.n) * 4) % 32 == 0 ? 2 : ((size_t(d.n) * 4) % 16 == 0 ? 1 : 0);
+    const uint32_t fmt = d.ab_dtype == CUTE_B200_BF16 ? 1u : 0u;
+    p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(bn >> 3) << 17) | (uint32_t((BM * group) >> 4) << 24);
+
+    CUtensorMap tmA, tmB;
+    CB_TRY(make_tensor_map(&tmA, a, d.ab_dtype, d.m, d.k, BM * mh));
+    CB_TRY(make_tensor_map(&tmB, b, d.ab_dtype, d.n, d.k, bn / group));
+    cute_b200_status st = CUTE_B200_ERR_UNSUPPORTED;
+#define CB_CASE(G, N_, H, BF) \
+    if (group == G && bn == N_ && mh == H && !BF) st = launch<G, N_, H, false>(tmA, tmB, p, setup->sm_count, stream);
+    CB_GEMM_VARIANTS(CB_CASE)
+#undef CB_CASE
+    CB_TRY(st);
+    const unsigned blocks = unsigned((plane + 1023) / 1024);
+    if (c_bf16)
+        gemm_splitk_reduce<true><<<blocks, 256, 0, stream>>>(static_cast<const float *>(setup->scratch), splits, plane, plane,
+                                                             reinterpret_cast<void *>(c), d.alpha, d.beta);
+    else
+        gemm_splitk_reduce<false><<<blocks, 256, 0, stream>>>(static_cast<const float *>(setup->scratch), splits, plane, plane,
+                                                              reinterpret_cast<void *>(c), d.alpha, d.beta);
+    CB_CUDA(cudaGetLastError());
+    count_launch();
+    return CUTE_B200_OK;
+}
+
 void gemm_tn_release_scratch() {
     int device = 0;
     if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return;

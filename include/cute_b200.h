@@ -110,6 +110,43 @@ cute_b200_status cute_b200_gemm_tn_host(const cute_b200_gemm_desc *desc, const v
                                         double *seconds);
 cute_b200_status cute_b200_release_workspace(void);
 
+/* The split-k GEMM for callers that must not allocate device memory.  It has
+ * no counterpart in the reference crate.
+ *
+ * Who needs it: a process whose GPU memory is handed out by a pool it does not
+ * control (an inference server with a fixed memory budget, a framework that
+ * forbids raw cudaMalloc), a latency-critical loop that cannot afford the
+ * device-wide synchronisation cudaMalloc and cudaFree imply, or code that is
+ * already inside a region where allocation is not permitted.  For them the
+ * ordinary entry point is unsuitable as soon as the library decides to split
+ * k, because that path creates its scratch buffer on first need.
+ *
+ * This variant computes the same result (same tilings, same k ranges added in
+ * the same order, so the same bits as cute_b200_gemm_tn called with the same
+ * split_k) but takes its scratch from a 32 MiB array that is part of the
+ * library image.  Every GPU that loads the library holds those 32 MiB until
+ * the process exits.  It calls no cudaMalloc, cudaFree or other allocating
+ * routine, and it does not need cute_b200_init.
+ *
+ *   - split_k: 0 = choose, or 2..16; 1 is rejected (use cute_b200_gemm_tn).
+ *   - limit: m * n * 4 bytes * split_k must fit in 32 MiB (33 554 432 bytes),
+ *     e.g. 8192 x 128 in up to 8 ranges, 1024 x 1024 in up to 8; larger requests
+ *     return CUTE_B200_ERR_INVALID_ARGUMENT with the sizes in the message.
+ *     k must be positive and at least 128.
+ *   - the first call on each device resolves the array's device address and
+ *     raises the kernels' shared-memory limit (no allocation either); make that
+ *     first call before any stream capture begins.
+ *   - all calls share the one array and it keeps the previous call's partial
+ *     sums; every element a call reads was written by that same call, so
+ *     nothing needs clearing, but two calls whose kernels overlap on the GPU
+ *     (different streams, or concurrent host threads) race on it.  Serialise
+ *     them on one stream or with events.
+ *   - a bounded-wait report goes to the device's usual status word when the
+ *     device was set up with cute_b200_init, else to words private to this
+ *     entry point (first report wins and stays). */
+cute_b200_status cute_b200_gemm_tn_static(const cute_b200_gemm_desc *desc, uint64_t dA, uint64_t dB, uint64_t dC,
+                                          void *stream);
+
 /* ---- SIMT sgemm ------------------------------------------------------------
  * C = alpha * (A * B^T) + beta * C, all f32 and column-major: a[i + l*m],
  * b[j + l*n], c[i + j*m].  fma.rn.f32 accumulation with l ascending and a
