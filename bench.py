@@ -36,9 +36,9 @@ sys.path.insert(0, ROOT)
 METRIC = "bf16_gemm_tflops"
 UNIT = "TFLOP/s"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
-# DRAM bytes (read + write) of one 8192^3 bf16->bf16 launch of gemm_tn_kernel from the
-# ncu capture summarised in profiles/gemm_tn_8192_bf16_ncu.md; None until captured.
-NCU_TRAFFIC_8192 = None
+# DRAM bytes (read + write) of one 8192^3 bf16->bf16 launch of gemm_tn_kernel, from the
+# ncu capture summarised in profiles/gemm_tn_8192_bf16_ncu.md (831.0 MB + 120.3 MB).
+NCU_TRAFFIC_8192 = 951.3e6
 
 
 def peaks():
@@ -228,7 +228,7 @@ def main():
     per_gpu_tflops = value / world
     roofline = {"bound": "tensor", "achieved": per_gpu_tflops, "peak": pk[peak_kind], "unit": "TFLOP/s",
                 "frac": per_gpu_tflops / pk[peak_kind], "traffic": NCU_TRAFFIC_8192 if world == 1 else None,
-                "kernel": "gemm_tn_kernel<cta_group 2, tile 256x256x64>", "peak_kind": f"{peak_kind} ({pk['_source']})",
+                "kernel": "gemm_tn_kernel<cta_group 2, BN 256, MH 2>: 512x256 pair tile, BK 64, 4-stage TMA ring", "peak_kind": f"{peak_kind} ({pk['_source']})",
                 "frac_of_nominal_2250": per_gpu_tflops / 2250.0,
                 "algorithmic_flop_per_launch": 2.0 * rows * N * K}
 
