@@ -27,7 +27,7 @@
 // loads its own 128 rows of A and its own half of the B rows, the leader CTA
 // issues tcgen05.mma.cta_group::2 reading both shared memories, and each CTA
 // ends up with its 128 rows of the result in its own TMEM.  That halves the
-// B traffic per output.  The loads never use multicast.
+// B traffic per output.  Every CTA issues its own loads; none is shared.
 //
 // Every mbarrier wait has a time limit.  A waiter that gives up raises the
 // CTA's abort flag, writes a report to the device status word and all roles
