@@ -119,6 +119,7 @@ def run_reference(args):
         return
     import numpy as np
     import oracle
+    oracle.use_all_cores()
     w = workload(args.gpus)
     rows = 1024 if args.gpus == 1 else 256  # bounded sample: a band of rows of the same GEMM
     rng = np.random.default_rng(w["seed"])
@@ -346,6 +347,7 @@ def cpu_baseline(A, B, M, N, K):
     import numpy as np
     import torch
     import oracle
+    oracle.use_all_cores()
     rows = 2048
     a = A[:rows].view(torch.int16).cpu().numpy().view(np.uint16)
     b = B.view(torch.int16).cpu().numpy().view(np.uint16)

@@ -367,6 +367,33 @@ static cute_b200_status workspace_get(int device, int slot, size_t bytes, void *
     return CUTE_B200_OK;
 }
 
+// Streams and events of the host-buffer GEMM, created once per device.
+struct Pipeline {
+    static constexpr int kMaxPanels = 16;
+    bool ready = false;
+    cudaStream_t up = nullptr, compute = nullptr, down = nullptr;
+    cudaEvent_t uploaded[kMaxPanels], computed[kMaxPanels], t0[kMaxPanels], t1[kMaxPanels];
+};
+static Pipeline g_pipeline[kMaxDevices];
+
+static cute_b200_status pipeline_get(int device, Pipeline **out) {
+    Pipeline &p = g_pipeline[device];
+    if (!p.ready) {
+        CB_CUDA(cudaStreamCreateWithFlags(&p.up, cudaStreamNonBlocking));
+        CB_CUDA(cudaStreamCreateWithFlags(&p.compute, cudaStreamNonBlocking));
+        CB_CUDA(cudaStreamCreateWithFlags(&p.down, cudaStreamNonBlocking));
+        for (int i = 0; i < Pipeline::kMaxPanels; i++) {
+            CB_CUDA(cudaEventCreateWithFlags(&p.uploaded[i], cudaEventDisableTiming));
+            CB_CUDA(cudaEventCreateWithFlags(&p.computed[i], cudaEventDisableTiming));
+            CB_CUDA(cudaEventCreate(&p.t0[i]));
+            CB_CUDA(cudaEventCreate(&p.t1[i]));
+        }
+        p.ready = true;
+    }
+    *out = &p;
+    return CUTE_B200_OK;
+}
+
 cute_b200_status cute_b200_release_workspace(void) {
     int device = 0;
     if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) {
@@ -399,30 +426,60 @@ cute_b200_status cute_b200_gemm_tn_host(const cute_b200_gemm_desc *desc, const v
     CB_TRY(workspace_get(device, 0, a_bytes ? a_bytes : 16, &dA));
     CB_TRY(workspace_get(device, 1, b_bytes ? b_bytes : 16, &dB));
     CB_TRY(workspace_get(device, 2, c_bytes, &dC));
-    cudaStream_t stream = nullptr;
-    if (a_bytes) CB_CUDA(cudaMemcpyAsync(dA, hA, a_bytes, cudaMemcpyHostToDevice, stream));
-    if (b_bytes) CB_CUDA(cudaMemcpyAsync(dB, hB, b_bytes, cudaMemcpyHostToDevice, stream));
+    // Three streams pipeline the call over row panels of A and C: while panel i
+    // is multiplied, panel i+1 is on its way up and panel i-1 on its way down
+    // (PCIe is full duplex).  B has to be whole on the device before the first
+    // panel can run.
+    Pipeline *pipe = nullptr;
+    CB_TRY(pipeline_get(device, &pipe));
+    const size_t c_elem = desc->c_dtype == CUTE_B200_BF16 ? 2 : 4;
     const bool reads_c = !(desc->alpha == 1.0f && desc->beta == 0.0f);
-    if (reads_c) CB_CUDA(cudaMemcpyAsync(dC, hC, c_bytes, cudaMemcpyHostToDevice, stream));
-    cudaEvent_t e0 = nullptr, e1 = nullptr;
-    if (seconds) {
-        CB_CUDA(cudaEventCreate(&e0));
-        CB_CUDA(cudaEventCreate(&e1));
-        cudaEventRecord(e0, stream);
+    int panel_rows = ((desc->m / 8 + 511) / 512) * 512;
+    if (panel_rows < 1024) panel_rows = 1024;
+    int panels = (desc->m + panel_rows - 1) / panel_rows;
+    if (panels > Pipeline::kMaxPanels) {
+        panels = Pipeline::kMaxPanels;
+        panel_rows = (((desc->m + panels - 1) / panels + 511) / 512) * 512;
+        panels = (desc->m + panel_rows - 1) / panel_rows;
     }
-    cute_b200_status st = gemm_tn(*desc, reinterpret_cast<uint64_t>(dA), reinterpret_cast<uint64_t>(dB),
-                                  reinterpret_cast<uint64_t>(dC), stream, *dev);
-    if (seconds) cudaEventRecord(e1, stream);
-    if (st == CUTE_B200_OK) {
-        cudaError_t err = cudaMemcpyAsync(hC, dC, c_bytes, cudaMemcpyDeviceToHost, stream);
-        if (err != cudaSuccess) st = cuda_fail(err, "cudaMemcpyAsync");
+    if (b_bytes) CB_CUDA(cudaMemcpyAsync(dB, hB, b_bytes, cudaMemcpyHostToDevice, pipe->up));
+    cute_b200_status st = CUTE_B200_OK;
+    for (int i = 0; i < panels && st == CUTE_B200_OK; i++) {
+        const int row0 = i * panel_rows;
+        const int rows = desc->m - row0 < panel_rows ? desc->m - row0 : panel_rows;
+        const size_t a_off = size_t(row0) * desc->k * 2, c_off = size_t(row0) * desc->n * c_elem;
+        const size_t a_len = size_t(rows) * desc->k * 2, c_len = size_t(rows) * desc->n * c_elem;
+        if (a_len)
+            CB_CUDA(cudaMemcpyAsync(static_cast<char *>(dA) + a_off, static_cast<const char *>(hA) + a_off, a_len,
+                                    cudaMemcpyHostToDevice, pipe->up));
+        if (reads_c)
+            CB_CUDA(cudaMemcpyAsync(static_cast<char *>(dC) + c_off, static_cast<const char *>(hC) + c_off, c_len,
+                                    cudaMemcpyHostToDevice, pipe->up));
+        CB_CUDA(cudaEventRecord(pipe->uploaded[i], pipe->up));
+        CB_CUDA(cudaStreamWaitEvent(pipe->compute, pipe->uploaded[i], 0));
+        cute_b200_gemm_desc d = *desc;
+        d.m = rows;
+        if (seconds) CB_CUDA(cudaEventRecord(pipe->t0[i], pipe->compute));
+        st = gemm_tn(d, reinterpret_cast<uint64_t>(dA) + a_off, reinterpret_cast<uint64_t>(dB),
+                     reinterpret_cast<uint64_t>(dC) + c_off, pipe->compute, *dev);
+        if (st != CUTE_B200_OK) break;
+        if (seconds) CB_CUDA(cudaEventRecord(pipe->t1[i], pipe->compute));
+        CB_CUDA(cudaEventRecord(pipe->computed[i], pipe->compute));
+        CB_CUDA(cudaStreamWaitEvent(pipe->down, pipe->computed[i], 0));
+        CB_CUDA(cudaMemcpyAsync(static_cast<char *>(hC) + c_off, static_cast<char *>(dC) + c_off, c_len,
+                                cudaMemcpyDeviceToHost, pipe->down));
     }
-    if (st == CUTE_B200_OK) st = sync_and_check();
-    if (seconds) {
-        float ms = 0.0f;
-        if (st == CUTE_B200_OK && cudaEventElapsedTime(&ms, e0, e1) == cudaSuccess) *seconds = double(ms) * 1e-3;
-        cudaEventDestroy(e0);
-        cudaEventDestroy(e1);
+    {
+        const cute_b200_status sync = sync_and_check();  // waits for all three streams (device-wide)
+        if (st == CUTE_B200_OK) st = sync;
+    }
+    if (seconds && st == CUTE_B200_OK) {
+        double total = 0.0;
+        for (int i = 0; i < panels; i++) {
+            float ms = 0.0f;
+            if (cudaEventElapsedTime(&ms, pipe->t0[i], pipe->t1[i]) == cudaSuccess) total += double(ms) * 1e-3;
+        }
+        *seconds = total;
     }
     return st;
 }

@@ -40,6 +40,8 @@ def lib() -> ctypes.CDLL:
             getattr(L, name).argtypes = [vp, vp, sz]
             getattr(L, name).restype = None
         L.oracle_num_threads.restype = i
+        L.oracle_set_num_threads.argtypes = [i]
+        L.oracle_set_num_threads.restype = None
         L.oracle_elementwise_add_f32.argtypes = [vp, vp, vp, sz]
         L.oracle_elementwise_add_f32.restype = None
         L.oracle_gemm_tn.argtypes = [i, i, sz, sz, sz, vp, vp, vp, f, f, sz, sz]
@@ -66,6 +68,15 @@ def _c(a, dtype) -> np.ndarray:
 
 def num_threads() -> int:
     return int(lib().oracle_num_threads())
+
+
+def use_all_cores() -> int:
+    """Let OpenMP use every core this process may run on (overrides an
+    inherited OMP_NUM_THREADS); returns the thread count now in effect."""
+    import os
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().oracle_set_num_threads(n)
+    return num_threads()
 
 
 def f32_to_f16_bits(x) -> np.ndarray:

@@ -123,6 +123,16 @@ ORACLE_API void oracle_bf16_to_f32(const uint16_t *src, float *dst, size_t n) {
     for (size_t i = 0; i < n; i++) dst[i] = bf16_to_f32(src[i]);
 }
 
+/* torchrun exports OMP_NUM_THREADS=1; the timed CPU baseline asks for the
+ * host's cores explicitly. */
+ORACLE_API void oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 ORACLE_API int oracle_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();
