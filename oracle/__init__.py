@@ -23,8 +23,36 @@ def build(force: bool = False) -> str:
     """Compile ``oracle.c`` into ``liboracle.so`` (gcc + OpenMP) if needed."""
     src = os.path.join(_HERE, "oracle.c")
     if force or not os.path.exists(_LIB_PATH) or os.path.getmtime(_LIB_PATH) < os.path.getmtime(src):
-        subprocess.run(["make", "-C", _HERE, "-s", "-B"], check=True)
+        subprocess.run(["make", "-C", _HERE, "-s", "-B", "liboracle.so"], check=True)
     return _LIB_PATH
+
+
+_REF_PATH = os.path.join(_HERE, "libref_sm80.so")
+
+
+def build_ref_kernel(force: bool = False) -> str:
+    """Compile the restated reference GPU kernel (needs nvcc)."""
+    src = os.path.join(_HERE, "ref_kernel_sm80.cu")
+    if force or not os.path.exists(_REF_PATH) or os.path.getmtime(_REF_PATH) < os.path.getmtime(src):
+        subprocess.run(["make", "-C", _HERE, "-s", "-B", "libref_sm80.so"], check=True)
+    return _REF_PATH
+
+
+_ref = None
+
+
+def ref_tensorop_gemm(bf16: bool, m: int, n: int, k: int, dA: int, dB: int, dC: int, stream: int = 0) -> None:
+    """Launch the restated reference kernel (mma.sync, cp.async ring) on device
+    pointers: C f32 (m, n) = A (m, k) * B (n, k)^T."""
+    global _ref
+    if _ref is None:
+        build_ref_kernel()
+        _ref = ctypes.CDLL(_REF_PATH)
+        _ref.ref_tensorop_gemm.argtypes = [ctypes.c_int] * 4 + [ctypes.c_void_p] * 4
+        _ref.ref_tensorop_gemm.restype = ctypes.c_int
+    rc = _ref.ref_tensorop_gemm(int(bf16), m, n, k, dA, dB, dC, stream)
+    if rc != 0:
+        raise RuntimeError(f"ref_tensorop_gemm: cudaError {rc}")
 
 
 _lib = None
