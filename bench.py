@@ -267,25 +267,59 @@ def main():
         lib.release_workspace()
         del hA, hB, hC
 
-    # ---- optional replicated C (all-gather over NVLink), N > 1 only ----------------------
+    # ---- optional replicated C (exchange over NVLink), N > 1 only ---------------------------
     if world > 1 and not args.skip_extras:
+        from cute_rs_b200.sharded import RowShardedGemm
+        plan = RowShardedGemm(M, N, K, lib.BF16, lib.BF16, world, rank)
         full = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
-        for _ in range(2):
-            step()
-            dist.all_gather_into_tensor(full, C)
-        barrier()
-        e0.record()
         reps = max(3, min(args.steps, 10))
-        for _ in range(reps):
+
+        def timed(fn):
+            for _ in range(2):
+                fn()
+            barrier()
+            e0.record()
+            for _ in range(reps):
+                fn()
+            e1.record()
+            barrier()
+            tt = torch.tensor([e0.elapsed_time(e1) / reps], device="cuda", dtype=torch.float64)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            return float(tt.item())
+
+        def gemm_then_gather():
             step()
             dist.all_gather_into_tensor(full, C)
-        e1.record()
-        barrier()
-        tt = torch.tensor([e0.elapsed_time(e1) / reps], device="cuda", dtype=torch.float64)
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        out["replicated"] = {"value": flop / (float(tt.item()) * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": float(tt.item()),
-                             "collective": "ncclAllGather of the bf16 row blocks of C after the GEMM"}
+
+        comm_stream = torch.cuda.Stream()
+        ms_seq = timed(gemm_then_gather)
+        ms_ovl = timed(lambda: plan.launch_replicated(A.data_ptr(), B.data_ptr(), full, panels=8, comm_stream=comm_stream))
+        check = bool(torch.equal(full[row_begin:row_begin + rows], C))
+        # peer-to-peer pushes (CUDA IPC mappings, copy engines) instead of NCCL kernels
+        from cute_rs_b200.sharded import PeerBuffer, launch_replicated_p2p
         del full
+        peer_c = PeerBuffer(M * N * 2, world, rank)
+        full = peer_c.tensor((M, N), torch.bfloat16)
+        ms_p2p = timed(lambda: launch_replicated_p2p(plan, A.data_ptr(), B.data_ptr(), peer_c, 2, panels=8,
+                                                     copy_stream=comm_stream))
+        ref_full = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        dist.all_gather_into_tensor(ref_full, C)
+        check_p2p = bool(torch.equal(full, ref_full))
+        del ref_full
+        out["replicated"] = {
+            "unit": UNIT,
+            "gemm_then_all_gather": {"value": flop / (ms_seq * 1e-3) / 1e12, "ms_per_step": ms_seq,
+                                     "collective": "one ncclAllGather of the bf16 row blocks of C after the GEMM"},
+            "overlapped_panels": {"value": flop / (ms_ovl * 1e-3) / 1e12, "ms_per_step": ms_ovl,
+                                  "collective": "8 row panels; each is sent to the peers (NCCL send/recv) while the next is multiplied",
+                                  "own_rows_match_compute_only": check},
+            "peer_copies": {"value": flop / (ms_p2p * 1e-3) / 1e12, "ms_per_step": ms_p2p,
+                            "collective": "8 row panels; each is pushed into every peer's C with device-to-device copies over "
+                                          "NVLink (CUDA IPC mappings, copy engines, no NCCL) while the next is multiplied; "
+                                          "includes the closing barrier",
+                            "equals_all_gather_result": check_p2p}}
+        del full
+        peer_c.close()
 
     # ---- secondary kernels and the CPU baseline: rank 0 of a 1-GPU run only ----------------
     if world == 1 and not args.skip_extras:

@@ -28,7 +28,8 @@ EXPORTS = (
     "cute_b200_gemm_tn_host", "cute_b200_release_workspace", "cute_b200_gemm_tn_static",
     "cute_b200_elementwise_add_f32", "cute_b200_launch", "cute_b200_launch_host", "cute_b200_upload",
     "cute_b200_download", "cute_b200_free", "cute_b200_synchronize", "cute_b200_shard_rows",
-    "cute_b200_gemm_tn_shard", "cute_b200_device_status", "cute_b200_launch_count",
+    "cute_b200_gemm_tn_shard", "cute_b200_device_status", "cute_b200_launch_count", "cute_b200_alloc",
+    "cute_b200_ipc_export", "cute_b200_ipc_open", "cute_b200_ipc_close", "cute_b200_copy_async",
 )
 
 
@@ -87,6 +88,11 @@ def load() -> ctypes.CDLL:
     L.cute_b200_download.argtypes = [u64, vp, u64]
     L.cute_b200_free.argtypes = [u64]
     L.cute_b200_synchronize.argtypes = []
+    L.cute_b200_alloc.argtypes = [u64, ctypes.POINTER(u64)]
+    L.cute_b200_ipc_export.argtypes = [u64, ctypes.c_char_p]
+    L.cute_b200_ipc_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(u64)]
+    L.cute_b200_ipc_close.argtypes = [u64]
+    L.cute_b200_copy_async.argtypes = [u64, u64, u64, vp]
     L.cute_b200_shard_rows.argtypes = [i32, i32, i32, ctypes.POINTER(i32), ctypes.POINTER(i32)]
     L.cute_b200_gemm_tn_shard.argtypes = [ctypes.POINTER(GemmDesc), i32, i32, u64, u64, u64, i32, vp]
     L.cute_b200_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint32 * 4)]
@@ -191,6 +197,32 @@ def download(device: int, host_ptr: int, nbytes: int) -> None:
 
 def free(device: int) -> None:
     check(load().cute_b200_free(device))
+
+
+def alloc(nbytes: int) -> int:
+    out = ctypes.c_uint64()
+    check(load().cute_b200_alloc(nbytes, ctypes.byref(out)))
+    return out.value
+
+
+def ipc_export(device: int) -> bytes:
+    buf = ctypes.create_string_buffer(64)
+    check(load().cute_b200_ipc_export(device, buf))
+    return buf.raw
+
+
+def ipc_open(handle: bytes) -> int:
+    out = ctypes.c_uint64()
+    check(load().cute_b200_ipc_open(handle, ctypes.byref(out)))
+    return out.value
+
+
+def ipc_close(device: int) -> None:
+    check(load().cute_b200_ipc_close(device))
+
+
+def copy_async(dst: int, src: int, nbytes: int, stream: int = 0) -> None:
+    check(load().cute_b200_copy_async(dst, src, nbytes, stream))
 
 
 def synchronize() -> None:

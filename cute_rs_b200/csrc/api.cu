@@ -622,6 +622,48 @@ cute_b200_status cute_b200_free(uint64_t device) {
 
 cute_b200_status cute_b200_synchronize(void) { return sync_and_check(); }
 
+cute_b200_status cute_b200_alloc(uint64_t bytes, uint64_t *device_out) {
+    if (!device_out) return fail(CUTE_B200_ERR_NULL_POINTER, "alloc: null output");
+    DeviceState *dev;
+    CB_TRY(current_device(&dev));
+    void *p = nullptr;
+    CB_CUDA(cudaMalloc(&p, bytes ? bytes : 1));
+    *device_out = reinterpret_cast<uint64_t>(p);
+    return CUTE_B200_OK;
+}
+
+cute_b200_status cute_b200_ipc_export(uint64_t device, uint8_t handle_out[64]) {
+    if (!device || !handle_out) return fail(CUTE_B200_ERR_NULL_POINTER, "ipc_export: null argument");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    cudaIpcMemHandle_t h;
+    CB_CUDA(cudaIpcGetMemHandle(&h, reinterpret_cast<void *>(device)));
+    memcpy(handle_out, &h, 64);
+    return CUTE_B200_OK;
+}
+
+cute_b200_status cute_b200_ipc_open(const uint8_t handle[64], uint64_t *device_out) {
+    if (!handle || !device_out) return fail(CUTE_B200_ERR_NULL_POINTER, "ipc_open: null argument");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, 64);
+    void *p = nullptr;
+    CB_CUDA(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+    *device_out = reinterpret_cast<uint64_t>(p);
+    return CUTE_B200_OK;
+}
+
+cute_b200_status cute_b200_ipc_close(uint64_t device) {
+    if (device) CB_CUDA(cudaIpcCloseMemHandle(reinterpret_cast<void *>(device)));
+    return CUTE_B200_OK;
+}
+
+cute_b200_status cute_b200_copy_async(uint64_t dst, uint64_t src, uint64_t bytes, void *stream) {
+    if (bytes && (!dst || !src)) return fail(CUTE_B200_ERR_NULL_POINTER, "copy_async: null argument");
+    if (bytes)
+        CB_CUDA(cudaMemcpyAsync(reinterpret_cast<void *>(dst), reinterpret_cast<const void *>(src), bytes,
+                                cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream)));
+    return CUTE_B200_OK;
+}
+
 cute_b200_status cute_b200_shard_rows(int32_t m, int32_t world, int32_t rank, int32_t *row_begin, int32_t *rows) {
     if (!row_begin || !rows) return fail(CUTE_B200_ERR_NULL_POINTER, "shard_rows: null output");
     if (m < 0 || world <= 0 || rank < 0 || rank >= world)

@@ -41,3 +41,141 @@ class RowShardedGemm:
             if r == self.rank:
                 view.copy_(c_block)
             dist.broadcast(view, src=r, group=group)
+
+    def panels(self, count: int = 8):
+        """Row panels of this rank's block as (first row within the block, rows):
+        whole 128-row tiles, at most `count` of them."""
+        tiles = (self.rows + 127) // 128
+        count = max(1, min(count, tiles))
+        per = ((tiles + count - 1) // count) * 128
+        return [(r, min(per, self.rows - r)) for r in range(0, self.rows, per)]
+
+    def launch_replicated(self, dA_shard: int, dB: int, full, panels: int = 8, comm_stream=None, group=None,
+                          compute_panel=None) -> None:
+        """C replicated on every GPU, with the exchange hidden behind the math.
+
+        This rank's block is computed panel by panel straight into its rows of
+        `full` (m, n); as soon as a panel is done it is sent to every peer and the
+        peers' matching panels are received into their rows, on a second stream,
+        while the next panel is being multiplied.  Needs an even split (every rank
+        the same number of rows); a ragged split falls back to GEMM + all_gather.
+        `compute_panel(first_row_in_block, rows)` replaces the GEMM launch (tests).
+        """
+        import torch
+        import torch.distributed as dist
+        k_bytes = self.k * 2
+        c_elem = full.element_size()
+
+        def gemm_panel(r0, rows):
+            d = _lib.gemm_desc(rows, self.n, self.k, self.desc.ab_dtype, self.desc.c_dtype, self.desc.alpha,
+                               self.desc.beta)
+            stream = torch.cuda.current_stream().cuda_stream
+            _lib.gemm_tn(d, dA_shard + r0 * k_bytes, dB,
+                         full.data_ptr() + (self.row_begin + r0) * self.n * c_elem, stream)
+
+        run = compute_panel or gemm_panel
+        if not self.even() or self.world == 1:
+            for r0, rows in self.panels(1):
+                run(r0, rows)
+            if self.world > 1:
+                self.all_gather(full[self.row_begin:self.row_begin + self.rows].clone(), full, group=group)
+            return
+        on_gpu = full.is_cuda
+        comm = comm_stream or (torch.cuda.Stream() if on_gpu else None)
+        pending = []
+        for r0, rows in self.panels(panels):
+            run(r0, rows)
+            ops = []
+            for peer in range(self.world):
+                if peer == self.rank:
+                    continue
+                mine = full[self.row_begin + r0:self.row_begin + r0 + rows]
+                theirs = full[self.spans[peer][0] + r0:self.spans[peer][0] + r0 + rows]
+                ops.append(dist.P2POp(dist.isend, mine, peer, group=group))
+                ops.append(dist.P2POp(dist.irecv, theirs, peer, group=group))
+            if on_gpu:
+                done = torch.cuda.Event()
+                done.record()
+                with torch.cuda.stream(comm):
+                    comm.wait_event(done)
+                    pending += dist.batch_isend_irecv(ops)
+            else:
+                pending += dist.batch_isend_irecv(ops)
+        for req in pending:
+            req.wait()
+        if on_gpu:
+            torch.cuda.current_stream().wait_stream(comm)
+
+
+class PeerBuffer:
+    """A device buffer of the same size on every rank, each rank's copy mapped
+    into every other rank's address space (CUDA IPC over NVLink).
+
+    `ptrs[r]` is rank r's copy as seen from this process; `tensor(...)` views
+    this rank's own copy as a torch tensor.  Collective: every rank of `group`
+    must construct it at the same time.
+    """
+
+    def __init__(self, nbytes: int, world: int, rank: int, group=None):
+        import torch.distributed as dist
+        self.nbytes, self.world, self.rank = nbytes, world, rank
+        self.local = _lib.alloc(nbytes)
+        handles = [None] * world
+        dist.all_gather_object(handles, _lib.ipc_export(self.local), group=group)
+        self.ptrs = [self.local if r == rank else _lib.ipc_open(handles[r]) for r in range(world)]
+        dist.barrier(group=group)
+
+    def tensor(self, shape, dtype):
+        import torch
+
+        class _View:  # torch reads device memory it does not own through this protocol
+            pass
+
+        v = _View()
+        typestr = {torch.bfloat16: "<u2", torch.float16: "<f2", torch.float32: "<f4"}[dtype]
+        v.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (self.local, False), "version": 3}
+        t = torch.as_tensor(v, device="cuda")
+        return t.view(torch.bfloat16) if dtype == torch.bfloat16 else t
+
+    def close(self, group=None) -> None:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.synchronize()
+        dist.barrier(group=group)
+        for r, p in enumerate(self.ptrs):
+            if r != self.rank:
+                _lib.ipc_close(p)
+        dist.barrier(group=group)
+        _lib.free(self.local)
+        self.ptrs = []
+
+
+def launch_replicated_p2p(plan: RowShardedGemm, dA_shard: int, dB: int, peer_c: PeerBuffer, c_elem: int, panels: int = 8,
+                          copy_stream=None, group=None) -> None:
+    """C replicated on every GPU by peer-to-peer copies hidden behind the math.
+
+    `peer_c` holds the full (m, n) C of every rank.  This rank multiplies its row
+    block panel by panel into its own copy; each finished panel is pushed into
+    the same rows of every peer's copy with device-to-device copies on a second
+    stream (copy engines over NVLink: no SM is taken from the GEMM, and no NCCL
+    kernel has to find room beside the persistent GEMM CTAs), while the next
+    panel is being multiplied.  Returns after all ranks' pushes have landed.
+    """
+    import torch
+    import torch.distributed as dist
+    copy_stream = copy_stream or torch.cuda.Stream()
+    compute = torch.cuda.current_stream()
+    row_bytes = plan.n * c_elem
+    for r0, rows in plan.panels(panels):
+        d = _lib.gemm_desc(rows, plan.n, plan.k, plan.desc.ab_dtype, plan.desc.c_dtype, plan.desc.alpha, plan.desc.beta)
+        off = (plan.row_begin + r0) * row_bytes
+        _lib.gemm_tn(d, dA_shard + r0 * plan.k * 2, dB, peer_c.local + off, compute.cuda_stream)
+        done = torch.cuda.Event()
+        done.record(compute)
+        copy_stream.wait_event(done)
+        for step in range(1, plan.world):  # start with the next rank so that the links are used evenly
+            peer = (plan.rank + step) % plan.world
+            _lib.copy_async(peer_c.ptrs[peer] + off, peer_c.local + off, rows * row_bytes, copy_stream.cuda_stream)
+    copy_stream.synchronize()
+    compute.synchronize()
+    dist.barrier(group=group)  # every rank's pushes into this GPU have landed

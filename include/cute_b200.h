@@ -217,6 +217,20 @@ cute_b200_status cute_b200_gemm_tn_shard(const cute_b200_gemm_desc *desc, int32_
                                          uint64_t dA_shard, uint64_t dB, uint64_t dC_base, int32_t c_is_full,
                                          void *stream);
 
+/* ---- peer memory for the replicated result --------------------------------
+ * One process per GPU: to let a GPU write its rows of C straight into the
+ * other GPUs' copies over NVLink, every process allocates its C with
+ * cute_b200_alloc, exports it, and opens the others' handles (CUDA IPC; the
+ * 64-byte handles travel over whatever channel the caller has, e.g. the
+ * torch.distributed store).  cute_b200_copy_async is a device-to-device copy
+ * on a stream (copy engines, no SM), local or to a peer mapping.  No
+ * counterpart in the reference (single GPU). */
+cute_b200_status cute_b200_alloc(uint64_t bytes, uint64_t *device_out);
+cute_b200_status cute_b200_ipc_export(uint64_t device, uint8_t handle_out[64]);
+cute_b200_status cute_b200_ipc_open(const uint8_t handle[64], uint64_t *device_out);
+cute_b200_status cute_b200_ipc_close(uint64_t device);
+cute_b200_status cute_b200_copy_async(uint64_t dst, uint64_t src, uint64_t bytes, void *stream);
+
 /* ---- bounded waits ----------------------------------------------------------
  * Every spin on an mbarrier inside the GEMM kernel has a time limit.  A CTA
  * that gives up records {code, role/stage, block index, parity} here and the

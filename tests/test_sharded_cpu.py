@@ -46,3 +46,34 @@ def test_two_ranks_partition_and_gather(tmp_path, m):
     mp.spawn(_worker, args=(world, _free_port(), m, 96, 64, str(tmp_path)), nprocs=world, join=True)
     spans = [np.load(tmp_path / f"ok{r}.npy") for r in range(world)]
     assert spans[0][0] == 0 and spans[0][1] == spans[1][0] and spans[1][1] == m
+
+
+def _worker_overlap(rank, world, port, m, n, k, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from cute_rs_b200 import _lib
+        from cute_rs_b200.sharded import RowShardedGemm
+        rng = np.random.default_rng(4)
+        a = oracle.f32_to_bf16_bits(rng.normal(0, 0.02, (m, k)).astype(np.float32))
+        b = oracle.f32_to_bf16_bits(rng.normal(0, 0.02, (n, k)).astype(np.float32))
+        plan = RowShardedGemm(m, n, k, _lib.BF16, _lib.F32, world, rank)
+        full = torch.zeros(m, n)
+
+        def compute_panel(r0, rows):  # the oracle stands in for the GPU kernel
+            lo = plan.row_begin + r0
+            full[lo:lo + rows] = torch.from_numpy(oracle.gemm_tn(a[lo:lo + rows], b, oracle.BF16))
+
+        plan.launch_replicated(0, 0, full, panels=3, compute_panel=compute_panel)
+        assert np.array_equal(full.numpy(), oracle.gemm_tn(a, b, oracle.BF16))
+        assert sum(r for _, r in plan.panels(3)) == plan.rows
+        np.save(os.path.join(out_dir, f"ov{rank}.npy"), np.array([1]))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("m", [1024, 640])
+def test_two_ranks_replicate_with_overlapped_panels(tmp_path, m):
+    """Even split (1024): panel-by-panel exchange; ragged split (640): falls back to one gather."""
+    mp.spawn(_worker_overlap, args=(2, _free_port(), m, 96, 64, str(tmp_path)), nprocs=2, join=True)
+    assert all((tmp_path / f"ov{r}.npy").exists() for r in range(2))
