@@ -300,8 +300,9 @@ def main():
         del full
         peer_c = PeerBuffer(M * N * 2, world, rank)
         full = peer_c.tensor((M, N), torch.bfloat16)
+        copy_streams = [torch.cuda.Stream() for _ in range(world - 1)]
         ms_p2p = timed(lambda: launch_replicated_p2p(plan, A.data_ptr(), B.data_ptr(), peer_c, 2, panels=8,
-                                                     copy_stream=comm_stream))
+                                                     copy_streams=copy_streams))
         ref_full = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
         dist.all_gather_into_tensor(ref_full, C)
         check_p2p = bool(torch.equal(full, ref_full))

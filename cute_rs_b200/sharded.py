@@ -151,19 +151,21 @@ class PeerBuffer:
 
 
 def launch_replicated_p2p(plan: RowShardedGemm, dA_shard: int, dB: int, peer_c: PeerBuffer, c_elem: int, panels: int = 8,
-                          copy_stream=None, group=None) -> None:
+                          copy_streams=None, group=None) -> None:
     """C replicated on every GPU by peer-to-peer copies hidden behind the math.
 
     `peer_c` holds the full (m, n) C of every rank.  This rank multiplies its row
     block panel by panel into its own copy; each finished panel is pushed into
-    the same rows of every peer's copy with device-to-device copies on a second
-    stream (copy engines over NVLink: no SM is taken from the GEMM, and no NCCL
-    kernel has to find room beside the persistent GEMM CTAs), while the next
-    panel is being multiplied.  Returns after all ranks' pushes have landed.
+    the same rows of every peer's copy with device-to-device copies, one stream
+    per peer so that several copy engines and all NVLink ports work at once (no
+    SM is taken from the GEMM, and no NCCL kernel has to find room beside the
+    persistent GEMM CTAs), while the next panel is being multiplied.  Returns
+    after all ranks' pushes have landed.
     """
     import torch
     import torch.distributed as dist
-    copy_stream = copy_stream or torch.cuda.Stream()
+    if copy_streams is None:
+        copy_streams = [torch.cuda.Stream() for _ in range(plan.world - 1)]
     compute = torch.cuda.current_stream()
     row_bytes = plan.n * c_elem
     for r0, rows in plan.panels(panels):
@@ -172,10 +174,12 @@ def launch_replicated_p2p(plan: RowShardedGemm, dA_shard: int, dB: int, peer_c: 
         _lib.gemm_tn(d, dA_shard + r0 * plan.k * 2, dB, peer_c.local + off, compute.cuda_stream)
         done = torch.cuda.Event()
         done.record(compute)
-        copy_stream.wait_event(done)
-        for step in range(1, plan.world):  # start with the next rank so that the links are used evenly
+        for step in range(1, plan.world):  # rank r talks to r+1, r+2, ...: every link carries one copy at a time
             peer = (plan.rank + step) % plan.world
-            _lib.copy_async(peer_c.ptrs[peer] + off, peer_c.local + off, rows * row_bytes, copy_stream.cuda_stream)
-    copy_stream.synchronize()
+            stream = copy_streams[(step - 1) % len(copy_streams)]
+            stream.wait_event(done)
+            _lib.copy_async(peer_c.ptrs[peer] + off, peer_c.local + off, rows * row_bytes, stream.cuda_stream)
+    for stream in copy_streams:
+        stream.synchronize()
     compute.synchronize()
     dist.barrier(group=group)  # every rank's pushes into this GPU have landed
