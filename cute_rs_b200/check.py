@@ -1,0 +1,299 @@
+"""Host-side protocol checker for the sm_100a GEMM pipeline.
+
+The reference crate race-checks its kernels by running them in a CPU
+simulator with per-byte shared-memory metadata, per-warp vector clocks and an
+mbarrier phase/transaction model (src/sim/exec.rs:35-53, 98-151, 870-1011,
+1545-1740, 1886-1922).  The hand-written tcgen05 kernel cannot run in that
+simulator, so this module restates the kernel's synchronisation protocol -
+who waits on, arrives on and commits to which mbarrier, and which agent reads
+or writes which shared-memory stage and TMEM half - and checks it with the
+same rules:
+
+* agents (producer thread, MMA-issuing thread, epilogue warps, and the two
+  asynchronous agents: the TMA unit and the tensor core) carry vector clocks;
+* a read of a resource must happen after its last write, a write after every
+  earlier read and write (read-after-write, write-after-read, write-after-write);
+* an mbarrier phase completes when its arrival count and its transaction count
+  both reach zero; a successful wait acquires everything released into that
+  phase; more bytes than expected, or a phase that completes while a copy that
+  reports to it is still uncounted, is an error;
+* the parity rule: a wait for phase n must succeed exactly when n + 1 phases
+  have completed; if the hardware test `completed % 2 != parity` would pass
+  with any other count, the parity aliases an older or newer phase
+  (src/sim/exec.rs:1648-1668);
+* nothing may be left blocked at the end (the simulator reports loops that do
+  not terminate; here: deadlock).
+
+`gemm_schedule` generates the per-agent programs of `gemm_tn_kernel` for a
+tiling (CTA group, ring stages, accumulator halves and buffers) and a list of
+work units; `mutations` name deliberate protocol bugs used by the tests to show
+that the checker sees them.  It checks the protocol, not the CUDA source.
+"""
+from __future__ import annotations
+
+import random
+from dataclasses import dataclass, field
+
+
+class ProtocolError(Exception):
+    def __init__(self, kind: str, message: str):
+        super().__init__(f"{kind}: {message}")
+        self.kind = kind
+
+
+# ---- vector clocks -------------------------------------------------------------
+class Clock(dict):
+    def join(self, other: "Clock") -> None:
+        for a, t in other.items():
+            if self.get(a, 0) < t:
+                self[a] = t
+
+    def knows(self, stamp) -> bool:
+        agent, tick = stamp
+        return self.get(agent, 0) >= tick
+
+    def copy(self) -> "Clock":
+        return Clock(self)
+
+
+@dataclass
+class Barrier:
+    name: str
+    count: int                      # arrivals per phase
+    pending: int = 0                # arrivals left in the current phase
+    tx: int = 0                     # bytes expected minus bytes landed
+    completed: int = 0              # phases completed so far
+    release: Clock = field(default_factory=Clock)
+    phase_clock: dict = field(default_factory=dict)  # phase index -> clock released into it
+
+    def __post_init__(self):
+        self.pending = self.count
+
+    def _maybe_complete(self):
+        if self.pending == 0 and self.tx == 0:
+            self.phase_clock[self.completed] = self.release
+            self.completed += 1
+            self.release = Clock()
+            self.pending = self.count
+        elif self.pending == 0 and self.tx < 0:
+            raise ProtocolError("tx", f"{self.name}: more bytes landed than expect_tx announced")
+
+    def arrive(self, clock: Clock, expect: int = 0):
+        if self.pending == 0:
+            raise ProtocolError("arrive", f"{self.name}: more arrivals than the barrier was initialised for")
+        self.tx += expect
+        self.release.join(clock)
+        self.pending -= 1
+        self._maybe_complete()
+
+    def complete_tx(self, clock: Clock, nbytes: int):
+        self.tx -= nbytes
+        self.release.join(clock)
+        self._maybe_complete()
+
+
+@dataclass
+class Resource:
+    name: str
+    write: tuple = None             # stamp (agent, tick) of the last write
+    reads: list = field(default_factory=list)
+
+
+class Machine:
+    def __init__(self):
+        self.clocks = {}
+        self.barriers = {}
+        self.resources = {}
+
+    def clock(self, agent) -> Clock:
+        return self.clocks.setdefault(agent, Clock())
+
+    def tick(self, agent):
+        c = self.clock(agent)
+        c[agent] = c.get(agent, 0) + 1
+        return (agent, c[agent])
+
+    def res(self, name) -> Resource:
+        return self.resources.setdefault(name, Resource(name))
+
+    # An access by `agent`, ordered after everything `after` (a clock) knows.
+    def write(self, agent, name, after: Clock):
+        c = self.clock(agent)
+        c.join(after)
+        r = self.res(name)
+        if r.write and not c.knows(r.write):
+            raise ProtocolError("race", f"{agent} writes {name} without being ordered after the write by {r.write[0]}")
+        for rd in r.reads:
+            if not c.knows(rd):
+                raise ProtocolError("race", f"{agent} overwrites {name} while {rd[0]} may still be reading it")
+        r.write, r.reads = self.tick(agent), []
+
+    def read(self, agent, name, after: Clock):
+        c = self.clock(agent)
+        c.join(after)
+        r = self.res(name)
+        if r.write is None:
+            raise ProtocolError("uninitialised", f"{agent} reads {name} before anything wrote it")
+        if not c.knows(r.write):
+            raise ProtocolError("race", f"{agent} reads {name} without being ordered after the write by {r.write[0]}")
+        r.reads.append(self.tick(agent))
+
+    def accumulate(self, agent, name, after: Clock, first: bool):
+        """Read-modify-write by the tensor core; `first` overwrites (accumulate flag 0)."""
+        if first:
+            self.write(agent, name, after)
+        else:
+            self.read(agent, name, after)
+            r = self.res(name)
+            r.write, r.reads = self.tick(agent), []
+
+
+# ---- programs --------------------------------------------------------------------
+# An op is a tuple; the first element names it:
+#   ("wait", barrier, phase)                 block until `phase` of the barrier completed, acquire it
+#   ("arrive", barrier) / ("expect", barrier, bytes)   arrive (with expect_tx)
+#   ("tma", cta, stage, bytes, barrier)      TMA writes the stage, bytes reported to barrier
+#   ("mma", [stage resources], [tmem resources], first)
+#   ("commit", barrier)                      arrival by the tensor core after all MMAs issued so far
+#   ("ld", tmem resource)                    epilogue warp reads a TMEM half
+def run(programs: dict, barriers: dict, seed: int = 0, tma_bytes_to=None) -> Machine:
+    m = Machine()
+    m.barriers = {n: Barrier(n, c) for n, c in barriers.items()}
+    pcs = {a: 0 for a in programs}
+    rng = random.Random(seed)
+    agents = list(programs)
+    while True:
+        progressed, done = False, True
+        rng.shuffle(agents)
+        for a in agents:
+            prog = programs[a]
+            while pcs[a] < len(prog):
+                done = False
+                op = prog[pcs[a]]
+                kind = op[0]
+                if kind == "wait":
+                    bar, phase = m.barriers[op[1]], op[2]
+                    if (bar.completed % 2) == (phase % 2):
+                        break  # the hardware test `completed % 2 != parity` fails: still blocked
+                    if bar.completed != phase + 1:
+                        raise ProtocolError("parity", f"{a} waits for phase {phase} of {op[1]} (parity {phase % 2}); the "
+                                                      f"test passes with {bar.completed} phases completed")
+                    if phase >= 0:
+                        m.clock(a).join(bar.phase_clock[phase])
+                elif kind == "arrive":
+                    m.tick(a)
+                    m.barriers[op[1]].arrive(m.clock(a))
+                elif kind == "expect":
+                    m.tick(a)
+                    m.barriers[op[1]].arrive(m.clock(a), expect=op[2])
+                elif kind == "tma":
+                    _, cta, stage, nbytes, bar = op
+                    agent = f"tma{cta}"
+                    m.write(agent, f"smem{cta}.{stage}", m.clock(a))
+                    m.barriers[bar].complete_tx(m.clock(agent), nbytes)
+                elif kind == "mma":
+                    _, stages, tmems, first = op
+                    for s in stages:
+                        m.read("umma", s, m.clock(a))
+                    for t in tmems:
+                        m.accumulate("umma", t, m.clock(a), first)
+                elif kind == "commit":
+                    m.clock("umma").join(m.clock(a))
+                    m.barriers[op[1]].arrive(m.clock("umma"))
+                elif kind == "ld":
+                    m.read(a, op[1], m.clock(a))
+                else:
+                    raise ValueError(op)
+                pcs[a] += 1
+                progressed = True
+        if done:
+            break
+        if not progressed:
+            stuck = {a: programs[a][pcs[a]] for a in agents if pcs[a] < len(programs[a])}
+            raise ProtocolError("deadlock", f"no agent can proceed: {stuck}")
+    for b in m.barriers.values():
+        if b.tx != 0:
+            raise ProtocolError("tx", f"{b.name}: {b.tx} bytes still expected at the end (expect_tx too large or a copy missing)")
+    return m
+
+
+# ---- the GEMM kernel's protocol ------------------------------------------------------
+def gemm_schedule(cta_group: int = 2, stages: int = 4, mh: int = 2, acc_bufs: int = 1, units=(8, 8, 8),
+                  stage_bytes: int = 48 * 1024, mutations=()):
+    """Programs and barriers of gemm_tn_kernel for one cluster.
+
+    `units` lists the k-block count of each work unit the cluster processes (0 =
+    an empty k range).  Mutations (protocol bugs for the tests):
+      "producer_skips_empty_wait"  the producer refills a stage without waiting for its release
+      "mma_skips_full_wait"        the MMA issuer does not wait for the loads
+      "mma_skips_tmem_wait"        ... nor for the epilogue to drain the accumulator
+      "epilogue_arrives_early"     a warp hands the TMEM half back before reading it
+      "expect_tx_short"            the leader announces one CTA's bytes instead of the group's
+      "wrong_empty_parity"         the producer starts with the parity of a full ring
+      "no_peer_commit"             the leader forgets to release the peer CTA's stages
+    """
+    mut = set(mutations)
+    ctas = range(cta_group)
+    barriers = {}
+    for s in range(stages):
+        barriers[f"full.{s}"] = 1  # on the leader; counts the bytes of the whole group
+        for c in ctas:
+            barriers[f"empty{c}.{s}"] = 1
+    for b in range(acc_bufs):
+        for c in ctas:
+            barriers[f"tfull{c}.{b}"] = 1
+        for h in range(mh):
+            barriers[f"tempty.{b}.{h}"] = 8 * cta_group  # one arrival per epilogue warp of the group
+    programs = {f"producer{c}": [] for c in ctas}
+    programs["mma"] = []
+    for c in ctas:
+        for w in range(8):
+            programs[f"epilogue{c}.{w}"] = []
+
+    fill = 0   # ring slots filled so far (same sequence in every role)
+    it = 0     # non-empty units so far
+    for kbs in units:
+        buf, use = it % acc_bufs, it // acc_bufs
+        for kb in range(kbs):
+            s, rnd = fill % stages, fill // stages
+            for c in ctas:
+                p = programs[f"producer{c}"]
+                if "producer_skips_empty_wait" not in mut:
+                    p.append(("wait", f"empty{c}.{s}", rnd - 1 + (1 if "wrong_empty_parity" in mut else 0)))
+                if c == 0:
+                    total = stage_bytes * (1 if "expect_tx_short" in mut else cta_group)
+                    p.append(("expect", f"full.{s}", total))
+                p.append(("tma", c, s, stage_bytes, f"full.{s}"))
+            mma = programs["mma"]
+            if "mma_skips_full_wait" not in mut:
+                mma.append(("wait", f"full.{s}", rnd))
+            for h in range(mh):
+                if kb == 0 and "mma_skips_tmem_wait" not in mut:
+                    mma.append(("wait", f"tempty.{buf}.{h}", use - 1))
+                mma.append(("mma", [f"smem{c}.{s}" for c in ctas], [f"tmem{c}.{buf}.{h}" for c in ctas], kb == 0))
+            for c in ctas:
+                if c == 0 or "no_peer_commit" not in mut:
+                    mma.append(("commit", f"empty{c}.{s}"))
+            fill += 1
+        if kbs > 0:
+            for c in ctas:
+                programs["mma"].append(("commit", f"tfull{c}.{buf}"))
+            for c in ctas:
+                for w in range(8):
+                    e = programs[f"epilogue{c}.{w}"]
+                    e.append(("wait", f"tfull{c}.{buf}", use))
+                    for h in range(mh):
+                        if "epilogue_arrives_early" in mut:
+                            e.append(("arrive", f"tempty.{buf}.{h}"))
+                        e.append(("ld", f"tmem{c}.{buf}.{h}"))
+                        if "epilogue_arrives_early" not in mut:
+                            e.append(("arrive", f"tempty.{buf}.{h}"))
+            it += 1
+    return programs, barriers
+
+
+def check_gemm(seeds=range(4), **kw) -> None:
+    """Run the schedule under several interleavings; raises ProtocolError on the first violation."""
+    programs, barriers = gemm_schedule(**kw)
+    for seed in seeds:
+        run(programs, barriers, seed=seed)
