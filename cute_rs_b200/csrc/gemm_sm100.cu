@@ -49,7 +49,12 @@ namespace {
 constexpr int BM = 128;        // rows of C per CTA = TMEM lanes
 constexpr int BK = 64;         // k per stage: 64 x 2 B = one 128-byte swizzle row
 constexpr int UMMA_K = 16;     // k per tcgen05.mma for 16-bit inputs
-constexpr int NUM_THREADS = 320;  // warp 0 TMA, warp 1 MMA + TMEM, warps 2-9 epilogue
+#ifndef EPI_GROUPS_BIG
+#define EPI_GROUPS_BIG 2  // measured: four groups (16 warps) are no faster than two on 8192^3 (0.699 vs 0.695 ms)
+#endif
+// warp 0 TMA, warp 1 MMA + TMEM, then EG groups of four epilogue warps.
+__host__ __device__ constexpr int epilogue_groups(int bn, int mh) { return (bn == 256 && mh == 2) ? EPI_GROUPS_BIG : 2; }
+__host__ __device__ constexpr int num_threads(int bn, int mh) { return 64 + 128 * epilogue_groups(bn, mh); }
 constexpr uint32_t RING_BYTES = 224 * 1024;
 constexpr uint32_t BAR_BYTES = 256;
 constexpr uint64_t WAIT_LIMIT_NS = 4ull * 1000 * 1000 * 1000;
@@ -234,10 +239,11 @@ __device__ __forceinline__ void store_chunk(const GemmParams &p, void *cbase, in
 }
 
 template <int CTA_GROUP, int BN, int MH, bool C_BF16>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(num_threads(BN, MH), 1)
     gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                    const GemmParams p) {
     using C = Cfg<CTA_GROUP, BN, MH>;
+    constexpr int EG = epilogue_groups(BN, MH);
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = ptx::smem_u32(smem_raw);
     const uint32_t ring = (raw + 1023u) & ~1023u;  // swizzle atoms need 1024-byte alignment
@@ -267,7 +273,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         for (int buf = 0; buf < 2; buf++) {
             ptx::mbar_init(tfull_bar(buf), 1);
             for (int h = 0; h < 2; h++)
-                ptx::mbar_init(tempty_bar(buf, h), 8 * CTA_GROUP);  // one arrival per epilogue warp of the pair
+                ptx::mbar_init(tempty_bar(buf, h), 4 * EG * CTA_GROUP);  // one arrival per epilogue warp of the pair
         }
         ptx::mbar_init(drain_bar, 1);
         *abort_flag = 0u;
@@ -408,12 +414,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         __syncwarp();
     } else {
         // ------------------------------------------------------------ epilogue
-        // Eight warps: warp w reads TMEM lane quarter w % 4 (the only one it may
-        // address) and, of every 128-row half, the 32-column chunks of parity e.
+        // EG groups of four warps: warp w reads TMEM lane quarter w % 4 (the only one
+        // it may address) and, of every 128-row half, every EG-th 32-column chunk.
         const uint32_t q = uint32_t(warp) & 3u;
         const int e = (warp - 2) >> 2;
-        constexpr int CH = BN / 64;       // chunks per half per warp
-        constexpr int ITEMS = MH * CH;    // even
+        constexpr int CH = BN / 32 / EG;  // chunks per half per warp
+        constexpr int ITEMS = MH * CH;
         const bool plain = (p.alpha == 1.0f && p.beta == 0.0f);
         bool ok = true;
         int it = 0;
@@ -434,7 +440,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             }
             const int row0 = (tc.tm * CTA_GROUP + int(rank)) * C::A_ROWS + int(q) * 32 + lane;
             const uint32_t taddr0 = tmem_base + ((q * 32u) << 16) + uint32_t(buf * C::ACC_COLS);
-            auto col_of = [&](int i) { return ((i % CH) * 2 + e) * 32; };
+            auto col_of = [&](int i) { return ((i % CH) * EG + e) * 32; };
             auto load = [&](int i, uint32_t(&v)[32]) {
                 if (have_acc) {
                     ptx::tmem_ld_32x32(taddr0 + uint32_t((i / CH) * BN + col_of(i)), v);
@@ -463,11 +469,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 #pragma unroll 1
             for (int i = 0; i < ITEMS; i += 2) {
                 if (have_acc) ptx::tmem_ld_wait(va);
-                load(i + 1, vb);
+                if (i + 1 < ITEMS) load(i + 1, vb);
                 finish(i, va);
-                if (have_acc) ptx::tmem_ld_wait(vb);
-                if (i + 2 < ITEMS) load(i + 2, va);
-                finish(i + 1, vb);
+                if (i + 1 < ITEMS) {
+                    if (have_acc) ptx::tmem_ld_wait(vb);
+                    if (i + 2 < ITEMS) load(i + 2, va);
+                    finish(i + 1, vb);
+                }
             }
         }
     }
@@ -613,7 +621,7 @@ cute_b200_status launch(const CUtensorMap &tmA, const CUtensorMap &tmB, GemmPara
 
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(unsigned(clusters * CTA_GROUP));
-    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.blockDim = dim3(num_threads(BN, MH));
     cfg.dynamicSmemBytes = C::SMEM_BYTES;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
