@@ -90,7 +90,8 @@ struct GemmParams {
     uint32_t idesc;
     int m_tiles, n_tiles, group_m;
     int c_vec_ok;  // C base and row pitch allow 16-byte (1) or 32-byte (2) accesses
-    int debug;     // timing experiments only: bit 0 skips the TMA loads, bit 1 skips the stores
+    int debug;     // measurements and tests only: bit 0 skips the TMA loads, bit 1 the stores, bit 2 makes the
+                   // producer issue nothing at all (every consumer wait then runs out), bit 3 shortens the limit
     int splits;              // k is cut into this many ranges, one work unit each (1 = no split)
     size_t split_stride;     // bytes between the partial-sum planes of consecutive ranges
     uint32_t *status;
@@ -116,7 +117,8 @@ __device__ __noinline__ void report_timeout(uint32_t *status, uint32_t where, ui
 
 // Wait for phase `parity` of `bar`.  false = gave up (limit or CTA abort).
 __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
-                                         uint32_t *status, uint32_t where, uint32_t detail) {
+                                         uint32_t *status, uint32_t where, uint32_t detail,
+                                         uint64_t limit_ns = WAIT_LIMIT_NS) {
     if (ptx::mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = ptx::globaltimer_ns();
     uint32_t spins = 0;
@@ -124,7 +126,7 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile
         if (ptx::mbar_try_wait(bar, parity)) return true;
         if ((++spins & 255u) == 0u) {
             if (*abort_flag) return false;
-            if (ptx::globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+            if (ptx::globaltimer_ns() - t0 > limit_ns) {
                 *abort_flag = 1u;
                 report_timeout(status, where, detail, parity);
                 return false;
@@ -264,6 +266,7 @@ __global__ void __launch_bounds__(num_threads(BN, MH), 1)
     const int num_units = p.m_tiles * p.n_tiles * p.splits;
     const int k_blocks = (p.K + BK - 1) / BK;
     constexpr int nstages = C::STAGES;
+    const uint64_t wait_limit = (p.debug & 8) ? 20ull * 1000 * 1000 : WAIT_LIMIT_NS;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; s++) {
@@ -301,13 +304,13 @@ __global__ void __launch_bounds__(num_threads(BN, MH), 1)
             uint32_t ph = 0;
             uint32_t filled = 0, filled_parity = 0;  // per stage: was it filled, and in which phase
             bool ok = true;
-            for (int t = cluster_id; t < num_units && ok; t += num_clusters) {
+            for (int t = cluster_id; t < num_units && ok && !(p.debug & 4); t += num_clusters) {
                 const Unit u = unit_of(t, p, k_blocks);
                 const TileCoord tc = tile_coord(u.tile, p);
                 const int row_a = (tc.tm * CTA_GROUP + int(rank)) * C::A_ROWS;
                 const int row_b = tc.tn * BN + int(rank) * C::B_ROWS;
                 for (int kb = u.kb0; kb < u.kb1; kb++) {
-                    if (!wait_bar(empty_bar(s), ph ^ 1u, abort_flag, p.status, WHERE_PRODUCER, uint32_t(s))) {
+                    if (!wait_bar(empty_bar(s), ph ^ 1u, abort_flag, p.status, WHERE_PRODUCER, uint32_t(s), wait_limit)) {
                         ok = false;
                         break;
                     }
@@ -362,7 +365,7 @@ __global__ void __launch_bounds__(num_threads(BN, MH), 1)
                 it++;
                 const uint32_t d_tmem = tmem_base + uint32_t(buf * C::ACC_COLS);
                 for (int kb = u.kb0; kb < u.kb1 && ok; kb++) {
-                    if (!wait_bar(full_bar(s), ph, abort_flag, p.status, WHERE_MMA_FULL, uint32_t(s))) {
+                    if (!wait_bar(full_bar(s), ph, abort_flag, p.status, WHERE_MMA_FULL, uint32_t(s), wait_limit)) {
                         ok = false;
                         break;
                     }
@@ -375,7 +378,7 @@ __global__ void __launch_bounds__(num_threads(BN, MH), 1)
                             // The epilogue must have drained this half of the buffer
                             // (a fresh barrier passes at once).
                             if (!wait_bar(tempty_bar(buf, h), aph ^ 1u, abort_flag, p.status, WHERE_MMA_TMEM,
-                                          uint32_t(buf * 2 + h))) {
+                                          uint32_t(buf * 2 + h), wait_limit)) {
                                 ok = false;
                                 break;
                             }
@@ -432,7 +435,7 @@ __global__ void __launch_bounds__(num_threads(BN, MH), 1)
             void *cbase = reinterpret_cast<uint8_t *>(p.C) + size_t(u.range) * p.split_stride;
             if (have_acc) {
                 it++;
-                if (!wait_bar(tfull_bar(buf), aph, abort_flag, p.status, WHERE_EPILOGUE, uint32_t(buf))) {
+                if (!wait_bar(tfull_bar(buf), aph, abort_flag, p.status, WHERE_EPILOGUE, uint32_t(buf), wait_limit)) {
                     ok = false;
                     break;
                 }

@@ -92,8 +92,9 @@ typedef struct {
     int32_t tile_m;    /* rows of C per CTA: 0 = choose; 128 or 256 */
     int32_t split_k;   /* k ranges computed as separate work units and summed by a second kernel through an
                           f32 scratch buffer the library allocates on first need: 0 = choose, 1 = never, <= 16 */
-    int32_t tuning[2]; /* zero.  Measurement knobs: [0] bit 0 skips the loads, bit 1 the stores (results are
-                          then meaningless); [1] row tiles walked per column step */
+    int32_t tuning[2]; /* zero.  Measurement and test knobs: [0] bit 0 skips the loads, bit 1 the stores (results
+                          are then meaningless), bits 2+3 make every in-kernel wait run out after 20 ms so that
+                          the bounded-wait report can be tested; [1] row tiles walked per column step */
 } cute_b200_gemm_desc;
 
 cute_b200_status cute_b200_gemm_tn(const cute_b200_gemm_desc *desc, uint64_t dA, uint64_t dB, uint64_t dC,
