@@ -268,58 +268,84 @@ def main():
         del hA, hB, hC
 
     # ---- optional replicated C (exchange over NVLink), N > 1 only ---------------------------
+    # Every variant leaves the whole C on every GPU.  They are timed interleaved, one step of each
+    # in turn, so that drift of the clocks under the power cap falls on all of them alike; a step
+    # is timed with CUDA events from its first launch to the point where the rank holds the peers'
+    # rows too (the variants that push into peer memory end with a barrier, which is inside).
     if world > 1 and not args.skip_extras:
-        from cute_rs_b200.sharded import RowShardedGemm
+        from cute_rs_b200.sharded import PeerBuffer, RowShardedGemm, launch_replicated_fused, launch_replicated_p2p
         plan = RowShardedGemm(M, N, K, lib.BF16, lib.BF16, world, rank)
-        full = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        full_nccl = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        peer_c = PeerBuffer(M * N * 2, world, rank)
+        full = peer_c.tensor((M, N), torch.bfloat16)
+        comm_stream = torch.cuda.Stream()
+        copy_streams = [torch.cuda.Stream() for _ in range(world - 1)]
         reps = max(3, min(args.steps, 10))
-
-        def timed(fn):
-            for _ in range(2):
-                fn()
-            barrier()
-            e0.record()
-            for _ in range(reps):
-                fn()
-            e1.record()
-            barrier()
-            tt = torch.tensor([e0.elapsed_time(e1) / reps], device="cuda", dtype=torch.float64)
-            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-            return float(tt.item())
 
         def gemm_then_gather():
             step()
-            dist.all_gather_into_tensor(full, C)
+            dist.all_gather_into_tensor(full_nccl, C)
 
-        comm_stream = torch.cuda.Stream()
-        ms_seq = timed(gemm_then_gather)
-        ms_ovl = timed(lambda: plan.launch_replicated(A.data_ptr(), B.data_ptr(), full, panels=8, comm_stream=comm_stream))
-        check = bool(torch.equal(full[row_begin:row_begin + rows], C))
-        # peer-to-peer pushes (CUDA IPC mappings, copy engines) instead of NCCL kernels
-        from cute_rs_b200.sharded import PeerBuffer, launch_replicated_p2p
-        del full
-        peer_c = PeerBuffer(M * N * 2, world, rank)
-        full = peer_c.tensor((M, N), torch.bfloat16)
-        copy_streams = [torch.cuda.Stream() for _ in range(world - 1)]
-        ms_p2p = timed(lambda: launch_replicated_p2p(plan, A.data_ptr(), B.data_ptr(), peer_c, 2, panels=8,
-                                                     copy_streams=copy_streams))
+        variants = {
+            "compute_only": step,
+            "gemm_then_all_gather": gemm_then_gather,
+            "overlapped_panels": lambda: plan.launch_replicated(A.data_ptr(), B.data_ptr(), full_nccl, panels=8,
+                                                                comm_stream=comm_stream),
+            "peer_copies": lambda: launch_replicated_p2p(plan, A.data_ptr(), B.data_ptr(), peer_c, 2, panels=8,
+                                                         copy_streams=copy_streams),
+            "fused_pusher_warp": lambda: launch_replicated_fused(plan, A.data_ptr(), B.data_ptr(), peer_c, 2),
+            "fused_pusher_warp_tile_m_128": lambda: launch_replicated_fused(plan, A.data_ptr(), B.data_ptr(), peer_c, 2, tile_m=128),
+            "fused_register_stores": lambda: launch_replicated_fused(plan, A.data_ptr(), B.data_ptr(), peer_c, 2, tile_m=128,
+                                                                     register_stores=True),
+        }
+        # correctness of each variant against the all-gather of the compute-only C
+        step()
         ref_full = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
         dist.all_gather_into_tensor(ref_full, C)
-        check_p2p = bool(torch.equal(full, ref_full))
+        equal = {}
+        for name, fn in variants.items():
+            if name == "compute_only":
+                continue
+            dst = full if name.startswith(("peer", "fused")) else full_nccl
+            dst.zero_()
+            barrier()
+            fn()
+            barrier()
+            equal[name] = bool(torch.equal(dst, ref_full))
         del ref_full
-        out["replicated"] = {
-            "unit": UNIT,
-            "gemm_then_all_gather": {"value": flop / (ms_seq * 1e-3) / 1e12, "ms_per_step": ms_seq,
-                                     "collective": "one ncclAllGather of the bf16 row blocks of C after the GEMM"},
-            "overlapped_panels": {"value": flop / (ms_ovl * 1e-3) / 1e12, "ms_per_step": ms_ovl,
-                                  "collective": "8 row panels; each is sent to the peers (NCCL send/recv) while the next is multiplied",
-                                  "own_rows_match_compute_only": check},
-            "peer_copies": {"value": flop / (ms_p2p * 1e-3) / 1e12, "ms_per_step": ms_p2p,
-                            "collective": "8 row panels; each is pushed into every peer's C with device-to-device copies over "
-                                          "NVLink (CUDA IPC mappings, copy engines, no NCCL) while the next is multiplied; "
-                                          "includes the closing barrier",
-                            "equals_all_gather_result": check_p2p}}
-        del full
+        sums = torch.zeros(len(variants), device="cuda", dtype=torch.float64)
+        for r in range(reps + 1):
+            for i, fn in enumerate(variants.values()):
+                barrier()
+                e0.record()
+                fn()
+                e1.record()
+                torch.cuda.synchronize()
+                if r > 0:  # the first round warms up
+                    sums[i] += e0.elapsed_time(e1)
+        sums /= reps
+        dist.all_reduce(sums, op=dist.ReduceOp.MAX)
+        how = {
+            "compute_only": "row blocks of C stay on their GPUs (the headline number's step, timed the same way)",
+            "gemm_then_all_gather": "one ncclAllGather of the bf16 row blocks of C after the GEMM",
+            "overlapped_panels": "8 row panels; each is sent to the peers (NCCL send/recv) while the next is multiplied",
+            "peer_copies": "8 row panels; each is pushed into every peer's C with device-to-device copies over NVLink "
+                           "(CUDA IPC mappings, copy engines, no NCCL) while the next is multiplied; closing barrier",
+            "fused_pusher_warp": "one GEMM launch that also writes every finished tile into the peers' C over NVLink peer "
+                                 "mappings: a pusher warp per CTA copies the tile by TMA (load from its own C in L2, bulk "
+                                 "tensor store to each peer) beside the next tiles' main loop; closing barrier",
+            "fused_pusher_warp_tile_m_128": "the same with 128 rows of C per CTA (double-buffered accumulators)",
+            "fused_register_stores": "one GEMM launch whose epilogue warps store every chunk to the peers' C from registers "
+                                     "(32 bytes per lane), 128 rows of C per CTA; closing barrier",
+        }
+        rep = {"unit": UNIT, "timing": "%d interleaved steps of each variant, CUDA events, max over ranks" % reps}
+        for i, name in enumerate(variants):
+            ms_v = float(sums[i].item())
+            rep[name] = {"value": flop / (ms_v * 1e-3) / 1e12, "ms_per_step": ms_v, "how": how[name]}
+            if name in equal:
+                rep[name]["equals_all_gather_result"] = equal[name]
+        out["replicated"] = rep
+        del full, full_nccl
         peer_c.close()
 
     # ---- secondary kernels and the CPU baseline: rank 0 of a 1-GPU run only ----------------

@@ -29,7 +29,7 @@ EXPORTS = (
     "cute_b200_elementwise_add_f32", "cute_b200_launch", "cute_b200_launch_host", "cute_b200_upload",
     "cute_b200_download", "cute_b200_free", "cute_b200_synchronize", "cute_b200_shard_rows",
     "cute_b200_gemm_tn_shard", "cute_b200_device_status", "cute_b200_launch_count", "cute_b200_alloc",
-    "cute_b200_ipc_export", "cute_b200_ipc_open", "cute_b200_ipc_close", "cute_b200_copy_async",
+    "cute_b200_ipc_export", "cute_b200_ipc_open", "cute_b200_ipc_close", "cute_b200_copy_async", "cute_b200_gemm_tn_multi",
 )
 
 
@@ -93,6 +93,7 @@ def load() -> ctypes.CDLL:
     L.cute_b200_ipc_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(u64)]
     L.cute_b200_ipc_close.argtypes = [u64]
     L.cute_b200_copy_async.argtypes = [u64, u64, u64, vp]
+    L.cute_b200_gemm_tn_multi.argtypes = [ctypes.POINTER(GemmDesc), u64, u64, ctypes.POINTER(u64), i32, vp]
     L.cute_b200_shard_rows.argtypes = [i32, i32, i32, ctypes.POINTER(i32), ctypes.POINTER(i32)]
     L.cute_b200_gemm_tn_shard.argtypes = [ctypes.POINTER(GemmDesc), i32, i32, u64, u64, u64, i32, vp]
     L.cute_b200_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint32 * 4)]
@@ -130,6 +131,12 @@ def gemm_desc(m, n, k, ab_dtype, c_dtype, alpha=1.0, beta=0.0, tile_n=0, cta_gro
 
 def gemm_tn(desc: GemmDesc, dA: int, dB: int, dC: int, stream: int = 0) -> None:
     check(load().cute_b200_gemm_tn(ctypes.byref(desc), dA, dB, dC, stream))
+
+
+def gemm_tn_multi(desc: GemmDesc, dA: int, dB: int, dC_list, stream: int = 0) -> None:
+    """GEMM whose epilogue writes the result to every address in dC_list (own C and peers')."""
+    arr = (ctypes.c_uint64 * len(dC_list))(*dC_list)
+    check(load().cute_b200_gemm_tn_multi(ctypes.byref(desc), dA, dB, arr, len(dC_list), stream))
 
 
 def gemm_tn_static(desc: GemmDesc, dA: int, dB: int, dC: int, stream: int = 0) -> None:

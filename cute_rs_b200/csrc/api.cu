@@ -484,6 +484,14 @@ cute_b200_status cute_b200_gemm_tn_host(const cute_b200_gemm_desc *desc, const v
     return st;
 }
 
+cute_b200_status cute_b200_gemm_tn_multi(const cute_b200_gemm_desc *desc, uint64_t dA, uint64_t dB, const uint64_t *dC_list,
+                                         int32_t count, void *stream) {
+    if (!desc) return fail(CUTE_B200_ERR_NULL_POINTER, "gemm_tn_multi: desc is null");
+    DeviceState *dev;
+    CB_TRY(current_device(&dev));
+    return gemm_tn_multi(*desc, dA, dB, dC_list, count, static_cast<cudaStream_t>(stream), *dev);
+}
+
 cute_b200_status cute_b200_gemm_tn_static(const cute_b200_gemm_desc *desc, uint64_t dA, uint64_t dB, uint64_t dC,
                                           void *stream) {
     if (!desc) return fail(CUTE_B200_ERR_NULL_POINTER, "gemm_tn_static: desc is null");

@@ -50,6 +50,8 @@ cute_b200_status sgemm_nt(int m, int n, int k, float alpha, float beta, const fl
                           cudaStream_t stream, const DeviceState &dev);
 cute_b200_status gemm_tn(const cute_b200_gemm_desc &desc, uint64_t a, uint64_t b, uint64_t c, cudaStream_t stream,
                          const DeviceState &dev);
+cute_b200_status gemm_tn_multi(const cute_b200_gemm_desc &desc, uint64_t a, uint64_t b, const uint64_t *c_list, int count,
+                               cudaStream_t stream, const DeviceState &dev);
 cute_b200_status gemm_tn_init(const DeviceState &dev);
 void gemm_tn_release_scratch();
 cute_b200_status gemm_tn_static(const cute_b200_gemm_desc &desc, uint64_t a, uint64_t b, uint64_t c, cudaStream_t stream,

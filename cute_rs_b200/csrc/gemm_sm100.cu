@@ -49,18 +49,29 @@ namespace {
 constexpr int BM = 128;        // rows of C per CTA = TMEM lanes
 constexpr int BK = 64;         // k per stage: 64 x 2 B = one 128-byte swizzle row
 constexpr int UMMA_K = 16;     // k per tcgen05.mma for 16-bit inputs
-#ifndef EPI_GROUPS_BIG
-#define EPI_GROUPS_BIG 2  // measured: four groups (16 warps) are no faster than two on 8192^3 (0.699 vs 0.695 ms)
-#endif
-// warp 0 TMA, warp 1 MMA + TMEM, then EG groups of four epilogue warps.
-__host__ __device__ constexpr int epilogue_groups(int bn, int mh) { return (bn == 256 && mh == 2) ? EPI_GROUPS_BIG : 2; }
-__host__ __device__ constexpr int num_threads(int bn, int mh) { return 64 + 128 * epilogue_groups(bn, mh); }
-constexpr uint32_t RING_BYTES = 224 * 1024;
+constexpr uint32_t RING_BYTES = 192 * 1024;
+constexpr uint32_t PUSH_BUF_BYTES = 16 * 1024;  // one chunk of a finished tile on its way to the other GPUs
+constexpr uint32_t STAGING_BYTES = 2 * PUSH_BUF_BYTES;
 constexpr uint32_t BAR_BYTES = 256;
 constexpr uint64_t WAIT_LIMIT_NS = 4ull * 1000 * 1000 * 1000;
 
 // Report codes written to the status word.
-enum : uint32_t { WHERE_PRODUCER = 1, WHERE_MMA_FULL = 2, WHERE_MMA_TMEM = 3, WHERE_EPILOGUE = 4, WHERE_DRAIN = 5 };
+enum : uint32_t {
+    WHERE_PRODUCER = 1,
+    WHERE_MMA_FULL = 2,
+    WHERE_MMA_TMEM = 3,
+    WHERE_EPILOGUE = 4,
+    WHERE_DRAIN = 5,
+    WHERE_PUSHER = 6
+};
+
+#ifndef EPI_GROUPS_BIG
+#define EPI_GROUPS_BIG 2  // measured: four groups (16 warps) are no faster than two on 8192^3 (0.699 vs 0.695 ms)
+#endif
+// warp 0 TMA, warp 1 MMA + TMEM, then EG groups of four epilogue warps, then the warp that pushes
+// finished tiles to other GPUs (idle unless the launch has several destinations).
+__host__ __device__ constexpr int epilogue_groups(int bn, int mh) { return (bn == 256 && mh == 2) ? EPI_GROUPS_BIG : 2; }
+__host__ __device__ constexpr int num_threads(int bn, int mh) { return 64 + 128 * epilogue_groups(bn, mh) + 32; }
 
 // CTA_GROUP: CTAs per MMA (1, or 2 = a cluster pair).  BN: columns of C per
 // tile (the MMA's N).  MH: 128-row accumulators per CTA (1 or 2); with MH == 2
@@ -78,7 +89,7 @@ struct Cfg {
     static constexpr int ACC_COLS = MH * BN;                        // TMEM columns of one accumulator set
     static constexpr int ACC_BUFS = (2 * ACC_COLS <= 512) ? 2 : 1;  // double buffered when it fits
     static constexpr uint32_t TMEM_COLS = (ACC_COLS * ACC_BUFS <= 256) ? 256 : 512;
-    static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + BAR_BYTES;
+    static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + STAGING_BYTES + 1024 + BAR_BYTES;
     static_assert(STAGES >= 2 && STAGES <= 12, "ring depth");
     static_assert(ACC_COLS * ACC_BUFS <= 512, "accumulators exceed TMEM");
 };
@@ -95,6 +106,19 @@ struct GemmParams {
     int splits;              // k is cut into this many ranges, one work unit each (1 = no split)
     size_t split_stride;     // bytes between the partial-sum planes of consecutive ranges
     uint32_t *status;
+    // Further copies of C that receive the same result (other GPUs' C over NVLink peer mappings).
+    // Plain epilogue, no k split.  push = 1: the pusher warp copies every finished tile from C to
+    // each of them by TMA (load from C, which is still in L2, then one bulk tensor store per copy);
+    // push = 0: the epilogue warps store every chunk to each of them from registers as well.
+    int extra_count;
+    void *extra_c[7];
+    int push;
+};
+
+// Tensor maps of C ([0]) and of its further copies, for the pusher warp: boxes of BN columns by
+// PUSH_BUF_BYTES / (BN * element size) rows, not swizzled.
+struct CMaps {
+    CUtensorMap m[8];
 };
 
 // Shared-memory matrix descriptor of a K-major tile stored as 128-byte rows
@@ -243,21 +267,25 @@ __device__ __forceinline__ void store_chunk(const GemmParams &p, void *cbase, in
 template <int CTA_GROUP, int BN, int MH, bool C_BF16>
 __global__ void __launch_bounds__(num_threads(BN, MH), 1)
     gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                   const GemmParams p) {
+                   const __grid_constant__ CMaps tmC, const GemmParams p) {
     using C = Cfg<CTA_GROUP, BN, MH>;
     constexpr int EG = epilogue_groups(BN, MH);
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = ptx::smem_u32(smem_raw);
     const uint32_t ring = (raw + 1023u) & ~1023u;  // swizzle atoms need 1024-byte alignment
-    const uint32_t bars = ring + C::STAGES * C::STAGE_BYTES;
+    const uint32_t staging = ring + C::STAGES * C::STAGE_BYTES;  // 1024-byte aligned: stages are multiples of 1 KiB
+    const uint32_t bars = staging + STAGING_BYTES;
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (C::STAGES + s); };
     auto tfull_bar = [&](int buf) { return bars + 8u * (2 * C::STAGES + buf); };
     auto tempty_bar = [&](int buf, int h) { return bars + 8u * (2 * C::STAGES + 2 + buf * 2 + h); };
     const uint32_t drain_bar = bars + 8u * (2 * C::STAGES + 6);
-    uint8_t *tail = smem_raw + (bars - raw) + 8u * (2 * C::STAGES + 7);
+    auto push_bar = [&](int b) { return bars + 8u * (2 * C::STAGES + 7 + b); };
+    uint8_t *tail = smem_raw + (bars - raw) + 8u * (2 * C::STAGES + 9);
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(tail);
     volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(tail + 4);
+    volatile uint32_t *tiles_stored = reinterpret_cast<volatile uint32_t *>(tail + 8);  // epilogue warps x tiles
+    static_assert(8u * (2 * C::STAGES + 9) + 12u <= BAR_BYTES, "barrier area");
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = CTA_GROUP == 1 ? 0u : ptx::cluster_ctarank();
@@ -279,7 +307,10 @@ __global__ void __launch_bounds__(num_threads(BN, MH), 1)
                 ptx::mbar_init(tempty_bar(buf, h), 4 * EG * CTA_GROUP);  // one arrival per epilogue warp of the pair
         }
         ptx::mbar_init(drain_bar, 1);
+        ptx::mbar_init(push_bar(0), 1);
+        ptx::mbar_init(push_bar(1), 1);
         *abort_flag = 0u;
+        *tiles_stored = 0u;
         ptx::fence_mbar_init();
     }
     if (warp == 1) {
@@ -415,7 +446,7 @@ __global__ void __launch_bounds__(num_threads(BN, MH), 1)
             }
         }
         __syncwarp();
-    } else {
+    } else if (warp < 2 + 4 * EG) {
         // ------------------------------------------------------------ epilogue
         // EG groups of four warps: warp w reads TMEM lane quarter w % 4 (the only one
         // it may address) and, of every 128-row half, every EG-th 32-column chunk.
@@ -463,7 +494,11 @@ __global__ void __launch_bounds__(num_threads(BN, MH), 1)
                         else ptx::mbar_arrive_cluster(ptx::mapa(tempty_bar(buf, i / CH), 0));
                     }
                 }
-                if (!(p.debug & 2)) store_chunk<C_BF16>(p, cbase, row0 + (i / CH) * BM, tc.tn * BN + col_of(i), v, plain);
+                if (p.debug & 2) return;
+                store_chunk<C_BF16>(p, cbase, row0 + (i / CH) * BM, tc.tn * BN + col_of(i), v, plain);
+                if (!p.push)
+                    for (int d = 0; d < p.extra_count; d++)
+                        store_chunk<C_BF16>(p, p.extra_c[d], row0 + (i / CH) * BM, tc.tn * BN + col_of(i), v, true);
             };
             // Two register buffers: the TMEM read of the next chunk is in flight
             // while the current one is converted and stored.
@@ -480,7 +515,76 @@ __global__ void __launch_bounds__(num_threads(BN, MH), 1)
                     finish(i + 1, vb);
                 }
             }
+            if (p.push) {
+                // This warp's part of the tile is in C: make the stores visible to the TMA unit
+                // (async proxy) and count the warp in for the pusher.
+                ptx::fence_proxy_async_global();
+                __syncwarp();
+                if (lane == 0) ptx::red_release_shared_add(ptx::smem_u32(const_cast<uint32_t *>(tiles_stored)), 1u);
+            }
         }
+    } else {
+        // -------------------------------------------------------------- pusher
+        // One thread copies every tile this CTA has finished from C (still in L2) to the further
+        // copies of C on other GPUs: a TMA load of a chunk of whole tile rows (BN columns, 512 bytes
+        // or more per row, the segments NVLink carries best) into one of two buffers, then one bulk
+        // tensor store per destination.  It runs behind the epilogue and beside the main loop of
+        // the following tiles; nothing but the end of the kernel waits for it.
+        if (p.push && lane == 0) {
+            constexpr int PUSH_ROWS = int(PUSH_BUF_BYTES) / (BN * (C_BF16 ? 2 : 4));
+            constexpr int CHUNKS = C::A_ROWS / PUSH_ROWS;
+            static_assert(PUSH_ROWS >= 8 && C::A_ROWS % PUSH_ROWS == 0, "push chunk shape");
+            for (int d = 0; d <= p.extra_count; d++) ptx::prefetch_tensormap(&tmC.m[d]);
+            const int my_tiles = cluster_id < num_units ? (num_units - cluster_id + num_clusters - 1) / num_clusters : 0;
+            const int total = my_tiles * CHUNKS;
+            const uint32_t stored_addr = ptx::smem_u32(const_cast<uint32_t *>(tiles_stored));
+            auto coords = [&](int g, int &row, int &col) {
+                const TileCoord tc = tile_coord(unit_of(cluster_id + (g / CHUNKS) * num_clusters, p, k_blocks).tile, p);
+                row = (tc.tm * CTA_GROUP + int(rank)) * C::A_ROWS + (g % CHUNKS) * PUSH_ROWS;
+                col = tc.tn * BN;
+            };
+            // All epilogue warps have stored tile number `j` of this CTA.  false = gave up.
+            auto tile_stored = [&](int j) -> bool {
+                const uint32_t want = uint32_t(j + 1) * uint32_t(4 * EG);
+                const uint64_t t0 = ptx::globaltimer_ns();
+                uint32_t spins = 0;
+                while (ptx::ld_acquire_shared(stored_addr) < want) {
+                    if ((++spins & 63u) == 0u) {
+                        if (*abort_flag) return false;
+                        if (ptx::globaltimer_ns() - t0 > wait_limit) {
+                            *abort_flag = 1u;
+                            report_timeout(p.status, WHERE_PUSHER, want, 0u);
+                            return false;
+                        }
+                    }
+                }
+                ptx::fence_proxy_async_global();
+                return true;
+            };
+            auto load = [&](int g) -> bool {
+                if (g % CHUNKS == 0 && !tile_stored(g / CHUNKS)) return false;
+                int row, col;
+                coords(g, row, col);
+                ptx::mbar_arrive_expect_tx(push_bar(g & 1), PUSH_BUF_BYTES);
+                ptx::tma_load_2d(staging + uint32_t(g & 1) * PUSH_BUF_BYTES, &tmC.m[0], push_bar(g & 1), col, row);
+                return true;
+            };
+            bool ok = total > 0 && load(0);
+            for (int g = 0; g < total && ok; g++) {
+                if (!wait_bar(push_bar(g & 1), uint32_t(g >> 1) & 1u, abort_flag, p.status, WHERE_PUSHER, uint32_t(g), wait_limit))
+                    break;
+                int row, col;
+                coords(g, row, col);
+                if (row < p.M)  // rows past the end of C are clipped by the TMA unit, whole chunks are skipped here
+                    for (int d = 1; d <= p.extra_count; d++)
+                        ptx::tma_store_2d(&tmC.m[d], staging + uint32_t(g & 1) * PUSH_BUF_BYTES, col, row);
+                ptx::bulk_commit();
+                ptx::bulk_wait_read<1>();  // the stores of chunk g - 1 have read the buffer that chunk g + 1 fills
+                if (g + 1 < total) ok = load(g + 1);
+            }
+            ptx::bulk_wait_all();
+        }
+        __syncwarp();
     }
 
     // ---------------------------------------------------------------- teardown
@@ -604,9 +708,27 @@ cute_b200_status make_tensor_map(CUtensorMap *tm, uint64_t base, int dtype, int 
     return CUTE_B200_OK;
 }
 
+// Row-major (m, n) C, f32 or bf16, in boxes of box_cols x box_rows elements, not swizzled.
+cute_b200_status make_tensor_map_c(CUtensorMap *tm, uint64_t base, bool bf16, int m, int n, int box_cols, int box_rows) {
+    EncodeTiledFn encode;
+    CB_TRY(encode_fn(&encode));
+    const cuuint64_t esize = bf16 ? 2 : 4;
+    const cuuint64_t dims[2] = {cuuint64_t(n), cuuint64_t(m)};
+    const cuuint64_t strides[1] = {cuuint64_t(n) * esize};
+    const cuuint32_t box[2] = {cuuint32_t(box_cols), cuuint32_t(box_rows)};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = encode(tm, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
+                              reinterpret_cast<void *>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(CUTE_B200_ERR_CUDA, "cuTensorMapEncodeTiled (C) failed: CUresult %d (m %d, n %d, box %d x %d)", int(r), m, n,
+                    box_cols, box_rows);
+    return CUTE_B200_OK;
+}
+
 template <int CTA_GROUP, int BN, int MH, bool C_BF16>
-cute_b200_status launch(const CUtensorMap &tmA, const CUtensorMap &tmB, GemmParams p, int sm_count,
-                        cudaStream_t stream) {
+cute_b200_status launch(const CUtensorMap &tmA, const CUtensorMap &tmB, const CMaps &tmC, GemmParams p,
+                        int sm_count, cudaStream_t stream) {
     using C = Cfg<CTA_GROUP, BN, MH>;
     const int tile_rows = BM * MH * CTA_GROUP;
     p.m_tiles = (p.M + tile_rows - 1) / tile_rows;
@@ -634,7 +756,7 @@ cute_b200_status launch(const CUtensorMap &tmA, const CUtensorMap &tmB, GemmPara
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    CB_CUDA(cudaLaunchKernelEx(&cfg, gemm_tn_kernel<CTA_GROUP, BN, MH, C_BF16>, tmA, tmB, p));
+    CB_CUDA(cudaLaunchKernelEx(&cfg, gemm_tn_kernel<CTA_GROUP, BN, MH, C_BF16>, tmA, tmB, tmC, p));
     count_launch();
     return CUTE_B200_OK;
 }
@@ -853,7 +975,7 @@ cute_b200_status gemm_tn_static(const cute_b200_gemm_desc &d, uint64_t a, uint64
     CB_TRY(make_tensor_map(&tmB, b, d.ab_dtype, d.n, d.k, bn / group));
     cute_b200_status st = CUTE_B200_ERR_UNSUPPORTED;
 #define CB_CASE(G, N_, H, BF) \
-    if (group == G && bn == N_ && mh == H && !BF) st = launch<G, N_, H, false>(tmA, tmB, p, setup->sm_count, stream);
+    if (group == G && bn == N_ && mh == H && !BF) st = launch<G, N_, H, false>(tmA, tmB, CMaps{}, p, setup->sm_count, stream);
     CB_GEMM_VARIANTS(CB_CASE)
 #undef CB_CASE
     CB_TRY(st);
@@ -883,6 +1005,40 @@ cute_b200_status gemm_tn_init(const DeviceState &) {
     CB_GEMM_VARIANTS(CB_SET)
 #undef CB_SET
     return CUTE_B200_OK;
+}
+
+// Extra destinations of the next gemm_tn call on this thread (set by gemm_tn_multi).
+static thread_local const uint64_t *t_extra_c = nullptr;
+static thread_local int t_extra_count = 0;
+
+cute_b200_status gemm_tn_multi(const cute_b200_gemm_desc &d, uint64_t a, uint64_t b, const uint64_t *c_list, int count,
+                               cudaStream_t stream, const DeviceState &dev) {
+    if (!c_list || count < 1 || count > 8)
+        return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "gemm_tn_multi: 1 to 8 destinations, got %d", count);
+    if (count > 1) {
+        if (!(d.alpha == 1.0f && d.beta == 0.0f))
+            return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "gemm_tn_multi: several destinations need alpha = 1, beta = 0");
+        if (d.split_k > 1)
+            return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "gemm_tn_multi: several destinations cannot be combined with split_k");
+        const uint64_t mask = d.c_dtype == CUTE_B200_BF16 ? 1u : 3u;
+        for (int i = 1; i < count; i++)
+            if (!c_list[i] || ((c_list[i] ^ c_list[0]) & 31u) || (c_list[i] & mask))
+                return fail(CUTE_B200_ERR_MISALIGNED, "gemm_tn_multi: destination %d is null or aligned differently from the first", i);
+    }
+    cute_b200_gemm_desc dd = d;
+    if (count > 1 && d.k == 0) {  // nothing to multiply: every destination is filled with zeros by its own launch
+        for (int i = 0; i < count; i++) CB_TRY(gemm_tn(dd, a, b, c_list[i], stream, dev));
+        return CUTE_B200_OK;
+    }
+    if (count > 1) {
+        dd.split_k = 1;
+    }
+    t_extra_c = c_list + 1;
+    t_extra_count = count - 1;
+    const cute_b200_status st = gemm_tn(dd, a, b, c_list[0], stream, dev);
+    t_extra_c = nullptr;
+    t_extra_count = 0;
+    return st;
 }
 
 cute_b200_status gemm_tn(const cute_b200_gemm_desc &d, uint64_t a, uint64_t b, uint64_t c, cudaStream_t stream,
@@ -937,6 +1093,8 @@ cute_b200_status gemm_tn(const cute_b200_gemm_desc &d, uint64_t a, uint64_t b, u
     p.group_m = d.tuning[1];
     p.splits = splits;
     p.split_stride = 0;
+    p.extra_count = t_extra_count;
+    for (int i = 0; i < t_extra_count; i++) p.extra_c[i] = reinterpret_cast<void *>(t_extra_c[i]);
     const size_t c_elem = c_bf16 ? 2 : 4;
     p.c_vec_ok = ((c & 15u) == 0 && (size_t(d.n) * c_elem) % 16 == 0) ? 1 : 0;
     if ((c & 31u) == 0 && (size_t(d.n) * c_elem) % 32 == 0) p.c_vec_ok = 2;
@@ -948,6 +1106,16 @@ cute_b200_status gemm_tn(const cute_b200_gemm_desc &d, uint64_t a, uint64_t b, u
     CUtensorMap tmA, tmB;
     CB_TRY(make_tensor_map(&tmA, a, d.ab_dtype, d.m, d.k, BM * mh));
     CB_TRY(make_tensor_map(&tmB, b, d.ab_dtype, d.n, d.k, bn / group));
+    // Several destinations: the pusher warp copies finished tiles by TMA when every C is 16-byte
+    // aligned with a 16-byte row pitch; otherwise the epilogue stores to each of them from registers.
+    CMaps tmC = {};
+    if (p.extra_count > 0 && splits == 1 && (c & 15u) == 0 && (size_t(d.n) * c_elem) % 16 == 0 && !(d.tuning[0] & 16)) {
+        const int box_rows = int(PUSH_BUF_BYTES) / (bn * int(c_elem));
+        CB_TRY(make_tensor_map_c(&tmC.m[0], c, c_bf16, d.m, d.n, bn, box_rows));
+        for (int i = 0; i < p.extra_count; i++)
+            CB_TRY(make_tensor_map_c(&tmC.m[i + 1], reinterpret_cast<uint64_t>(p.extra_c[i]), c_bf16, d.m, d.n, bn, box_rows));
+        p.push = 1;
+    }
 
     if (splits > 1) {
         // First pass: every k range writes an f32 plane of partial sums into the
@@ -964,7 +1132,7 @@ cute_b200_status gemm_tn(const cute_b200_gemm_desc &d, uint64_t a, uint64_t b, u
         q.c_vec_ok = (size_t(d.n) * 4) % 32 == 0 ? 2 : ((size_t(d.n) * 4) % 16 == 0 ? 1 : 0);
         cute_b200_status st = CUTE_B200_ERR_UNSUPPORTED;
 #define CB_CASE(G, N_, H, BF) \
-    if (group == G && bn == N_ && mh == H && !BF) st = launch<G, N_, H, false>(tmA, tmB, q, dev.sm_count, stream);
+    if (group == G && bn == N_ && mh == H && !BF) st = launch<G, N_, H, false>(tmA, tmB, tmC, q, dev.sm_count, stream);
         CB_GEMM_VARIANTS(CB_CASE)
 #undef CB_CASE
         CB_TRY(st);
@@ -980,7 +1148,7 @@ cute_b200_status gemm_tn(const cute_b200_gemm_desc &d, uint64_t a, uint64_t b, u
         return CUTE_B200_OK;
     }
 #define CB_CASE(G, N_, H, BF) \
-    if (group == G && bn == N_ && mh == H && c_bf16 == BF) return launch<G, N_, H, BF>(tmA, tmB, p, dev.sm_count, stream);
+    if (group == G && bn == N_ && mh == H && c_bf16 == BF) return launch<G, N_, H, BF>(tmA, tmB, tmC, p, dev.sm_count, stream);
     CB_GEMM_VARIANTS(CB_CASE)
 #undef CB_CASE
     return fail(CUTE_B200_ERR_UNSUPPORTED, "gemm_tn: no kernel for cta_group %d, tile %d x %d", group, BM * mh, bn);

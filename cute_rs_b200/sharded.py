@@ -183,3 +183,26 @@ def launch_replicated_p2p(plan: RowShardedGemm, dA_shard: int, dB: int, peer_c: 
         stream.synchronize()
     compute.synchronize()
     dist.barrier(group=group)  # every rank's pushes into this GPU have landed
+
+
+def launch_replicated_fused(plan: RowShardedGemm, dA_shard: int, dB: int, peer_c: PeerBuffer, c_elem: int, group=None,
+                            tile_m: int = 0, register_stores: bool = False) -> None:
+    """C replicated on every GPU by the GEMM kernel itself: one launch whose
+    epilogue warps store every finished tile into this rank's rows of its own C
+    and of every peer's C (peer mappings over NVLink), so the transfer rides
+    under the tensor-core work of the following tiles.  The stores are bulk
+    tensor (TMA) stores from a shared-memory staging buffer, one per destination
+    (``register_stores`` selects 32-byte stores straight from registers, which
+    NVLink carries less well).  No collective library is involved; the closing barrier only tells every rank that all peers' stores
+    into its C have completed."""
+    import torch
+    import torch.distributed as dist
+    off = plan.row_begin * plan.n * c_elem
+    dests = [peer_c.local + off] + [peer_c.ptrs[(plan.rank + s) % plan.world] + off for s in range(1, plan.world)]
+    d = _lib.gemm_desc(plan.rows, plan.n, plan.k, plan.desc.ab_dtype, plan.desc.c_dtype, tile_m=tile_m)
+    if register_stores:
+        d.tuning[0] |= 16
+    stream = torch.cuda.current_stream()
+    _lib.gemm_tn_multi(d, dA_shard, dB, dests, stream.cuda_stream)
+    stream.synchronize()
+    dist.barrier(group=group)

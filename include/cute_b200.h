@@ -94,7 +94,8 @@ typedef struct {
                           f32 scratch buffer the library allocates on first need: 0 = choose, 1 = never, <= 16 */
     int32_t tuning[2]; /* zero.  Measurement and test knobs: [0] bit 0 skips the loads, bit 1 the stores (results
                           are then meaningless), bits 2+3 make every in-kernel wait run out after 20 ms so that
-                          the bounded-wait report can be tested; [1] row tiles walked per column step */
+                          the bounded-wait report can be tested, bit 4 makes cute_b200_gemm_tn_multi store to its
+                          destinations from registers instead of by TMA; [1] row tiles walked per column step */
 } cute_b200_gemm_desc;
 
 cute_b200_status cute_b200_gemm_tn(const cute_b200_gemm_desc *desc, uint64_t dA, uint64_t dB, uint64_t dC,
@@ -231,6 +232,18 @@ cute_b200_status cute_b200_ipc_export(uint64_t device, uint8_t handle_out[64]);
 cute_b200_status cute_b200_ipc_open(const uint8_t handle[64], uint64_t *device_out);
 cute_b200_status cute_b200_ipc_close(uint64_t device);
 cute_b200_status cute_b200_copy_async(uint64_t dst, uint64_t src, uint64_t bytes, void *stream);
+
+/* The GEMM with its result written to several copies of C at once: dC_list[0]
+ * is normally this GPU's C, the others are peer mappings of the same rows in
+ * other GPUs' C (cute_b200_ipc_open).  The epilogue warps store every tile to
+ * all destinations, so the exchange that replicates C rides on NVLink while
+ * the tensor cores work on the next tile: compute and collective in one
+ * kernel, no NCCL call.  alpha must be 1 and beta 0; no k split; 1 <= count
+ * <= 8; every destination aligned like the first.  The caller makes the
+ * result visible to the peers the usual way (stream synchronisation followed
+ * by a barrier among the processes).  No counterpart in the reference. */
+cute_b200_status cute_b200_gemm_tn_multi(const cute_b200_gemm_desc *desc, uint64_t dA, uint64_t dB,
+                                         const uint64_t *dC_list, int32_t count, void *stream);
 
 /* ---- bounded waits ----------------------------------------------------------
  * Every spin on an mbarrier inside the GEMM kernel has a time limit.  A CTA

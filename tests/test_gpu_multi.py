@@ -25,7 +25,7 @@ def _worker(rank, world, port, m, n, k):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
         from cute_rs_b200 import _lib
-        from cute_rs_b200.sharded import PeerBuffer, RowShardedGemm, launch_replicated_p2p
+        from cute_rs_b200.sharded import PeerBuffer, RowShardedGemm, launch_replicated_fused, launch_replicated_p2p
         _lib.init(rank)
         rng = np.random.default_rng(4)
         a = oracle.f32_to_bf16_bits(rng.integers(-8, 9, (m, k)).astype(np.float32))
@@ -44,6 +44,13 @@ def _worker(rank, world, port, m, n, k):
         for _ in range(2):
             launch_replicated_p2p(plan, dA.data_ptr(), dB.data_ptr(), peer_c, 4, panels=3)
         assert np.array_equal(full.cpu().numpy(), want)
+        # the GEMM kernel's own epilogue stores into every peer's C
+        for tile_m, regs in ((0, False), (128, False), (0, True)):
+            full.zero_()
+            torch.cuda.synchronize()
+            dist.barrier()
+            launch_replicated_fused(plan, dA.data_ptr(), dB.data_ptr(), peer_c, 4, tile_m=tile_m, register_stores=regs)
+            assert np.array_equal(full.cpu().numpy(), want)
         peer_c.close()
         # NCCL send/recv per panel
         full2 = torch.zeros(m, n, device="cuda")

@@ -239,6 +239,52 @@ def test_gemm_ragged_shapes(lib, gpu, m, n, k, cdt_name, cta_group, tile_m):
         assert np.array_equal(got, want)
 
 
+@pytest.mark.parametrize("m,n,k", [(1, 8, 8), (100, 200, 72), (200, 136, 8), (129, 257, 520), (300, 520, 200), (128, 130, 64),
+                                   (512, 384, 1088), (64, 64, 0)])
+@pytest.mark.parametrize("cdt_name", ["f32", "bf16"])
+@pytest.mark.parametrize("cta_group,tile_m", [(0, 0), (1, 128), (2, 128), (2, 256)])
+@pytest.mark.parametrize("register_stores", [False, True])
+def test_gemm_several_destinations(lib, gpu, m, n, k, cdt_name, cta_group, tile_m, register_stores):
+    """gemm_tn_multi writes the same C to every destination, by TMA stores where the
+    row pitch allows them (a multiple of 16 bytes) and from registers otherwise."""
+    import torch
+    cdt = lib.F32 if cdt_name == "f32" else lib.BF16
+    a, b, _ = lcg_buffers([m * max(k, 1), n * max(k, 1), 0], small=True)
+    a_bits, b_bits = oracle.f32_to_bf16_bits(a[:m * k].reshape(m, k)), oracle.f32_to_bf16_bits(b[:n * k].reshape(n, k))
+    want = oracle.gemm_tn(a_bits, b_bits, lib.BF16, cdt)
+    np_c = np.float32 if cdt == lib.F32 else np.uint16
+    # a guard row after each destination shows stores that run past the end
+    dests = [dev(np.full((m + 1, n), 7, np_c)) for _ in range(3)]
+    dA, dB = dev(a_bits if k else np.zeros((1, 8), np.uint16)), dev(b_bits if k else np.zeros((1, 8), np.uint16))
+    d = lib.gemm_desc(m, n, k, lib.BF16, cdt, 1.0, 0.0, 0, cta_group, tile_m, 0)
+    if register_stores:
+        d.tuning[0] |= 16
+    lib.gemm_tn_multi(d, dA.data_ptr() if k else 0, dB.data_ptr() if k else 0, [t.data_ptr() for t in dests], 0)
+    torch.cuda.synchronize()
+    assert lib.device_status() == (0, 0, 0, 0)
+    for t in dests:
+        got = host(t, np_c).reshape(m + 1, n)
+        assert np.array_equal(got[:m], want)
+        assert np.all(got[m] == 7)
+
+
+def test_gemm_several_destinations_rejects_bad_arguments(lib, gpu):
+    import torch
+    c = torch.zeros(128 * 128 + 8, dtype=torch.float32, device="cuda")
+    ab = torch.zeros(128 * 64, dtype=torch.int16, device="cuda")
+    d = lib.gemm_desc(128, 128, 64, lib.BF16, lib.F32)
+    with pytest.raises(lib.CuteB200Error):
+        lib.gemm_tn_multi(d, ab.data_ptr(), ab.data_ptr(), [], 0)
+    with pytest.raises(lib.CuteB200Error):
+        lib.gemm_tn_multi(d, ab.data_ptr(), ab.data_ptr(), [c.data_ptr()] * 9, 0)
+    with pytest.raises(lib.CuteB200Error):  # second destination in another 32-byte phase
+        lib.gemm_tn_multi(d, ab.data_ptr(), ab.data_ptr(), [c.data_ptr(), c.data_ptr() + 4], 0)
+    with pytest.raises(lib.CuteB200Error):
+        lib.gemm_tn_multi(lib.gemm_desc(128, 128, 64, lib.BF16, lib.F32, 2.0, 0.0), ab.data_ptr(), ab.data_ptr(),
+                          [c.data_ptr(), c.data_ptr()], 0)
+    torch.cuda.synchronize()
+
+
 @pytest.mark.parametrize("cdt_name", ["f32", "bf16"])
 @pytest.mark.parametrize("alpha,beta", [(1.5, -0.5), (0.0, 1.0), (2.0, 0.0), (1.0, 1.0)])
 @pytest.mark.parametrize("tile_m", [128, 256])
