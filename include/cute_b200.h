@@ -235,13 +235,18 @@ cute_b200_status cute_b200_copy_async(uint64_t dst, uint64_t src, uint64_t bytes
 
 /* The GEMM with its result written to several copies of C at once: dC_list[0]
  * is normally this GPU's C, the others are peer mappings of the same rows in
- * other GPUs' C (cute_b200_ipc_open).  The epilogue warps store every tile to
- * all destinations, so the exchange that replicates C rides on NVLink while
- * the tensor cores work on the next tile: compute and collective in one
- * kernel, no NCCL call.  alpha must be 1 and beta 0; no k split; 1 <= count
- * <= 8; every destination aligned like the first.  The caller makes the
- * result visible to the peers the usual way (stream synchronisation followed
- * by a barrier among the processes).  No counterpart in the reference. */
+ * other GPUs' C (cute_b200_ipc_open).  The epilogue stores every tile to the
+ * first; a further warp of each CTA then copies the finished tile from there
+ * (it is still in L2) to every other destination with TMA loads and bulk
+ * tensor stores, while the tensor cores work on the next tiles: compute and
+ * collective in one kernel, no NCCL call.  That form needs every C 16-byte
+ * aligned with a row pitch that is a multiple of 16 bytes; otherwise the
+ * epilogue warps store to all destinations from registers (slower over
+ * NVLink).  alpha must be 1 and beta 0; no k split; 1 <= count <= 8; every
+ * destination aligned like the first (same offset within 32 bytes).  The
+ * caller makes the result visible to the peers the usual way (stream
+ * synchronisation followed by a barrier among the processes).  No counterpart
+ * in the reference. */
 cute_b200_status cute_b200_gemm_tn_multi(const cute_b200_gemm_desc *desc, uint64_t dA, uint64_t dB,
                                          const uint64_t *dC_list, int32_t count, void *stream);
 
