@@ -24,6 +24,16 @@ same rules:
 * nothing may be left blocked at the end (the simulator reports loops that do
   not terminate; here: deadlock).
 
+The several-destination form of the kernel adds a pusher thread per CTA: the
+epilogue warps store their part of a tile to C and publish their own tile
+count in a shared-memory slot (release), the pusher waits until every warp's
+slot has reached the tile (acquire),
+lets the TMA unit load the tile from C into one of two staging buffers
+(reported to an mbarrier), issues the bulk stores that read the buffer, and
+waits for the stores of the previous chunk to have read theirs before the
+buffer is filled again.  The counter, the bulk groups and the global-memory
+tile parts are modelled with the same clocks.
+
 `gemm_schedule` generates the per-agent programs of `gemm_tn_kernel` for a
 tiling (CTA group, ring stages, accumulator halves and buffers) and a list of
 work units; `mutations` name deliberate protocol bugs used by the tests to show
@@ -104,6 +114,8 @@ class Machine:
         self.clocks = {}
         self.barriers = {}
         self.resources = {}
+        self.counters = {}   # name -> [value, clock released into it]
+        self.groups = {}     # issuing agent -> list of bulk groups (each a clock of the reads it still does)
 
     def clock(self, agent) -> Clock:
         return self.clocks.setdefault(agent, Clock())
@@ -156,7 +168,18 @@ class Machine:
 #   ("mma", [stage resources], [tmem resources], first)
 #   ("commit", barrier)                      arrival by the tensor core after all MMAs issued so far
 #   ("ld", tmem resource)                    epilogue warp reads a TMEM half
-def run(programs: dict, barriers: dict, seed: int = 0, tma_bytes_to=None) -> Machine:
+#   ("st", resource)                         epilogue warp writes its part of a tile of C
+#   ("signal", counter)                      release-increment of a shared-memory counter
+#   ("wait_count", counter, value)           acquire-poll until the counter has reached value
+#   ("tma_load", cta, [C parts], buffer, bytes, barrier)   TMA reads the parts, writes the staging buffer
+#   ("tma_store", cta, buffer)               TMA reads the staging buffer (one bulk group per op)
+#   ("wait_read", keep)                      all but the newest `keep` bulk groups have read their source
+def run(programs: dict, barriers: dict, seed: int = 0, tma_bytes_to=None, max_burst: int = 0, stalls=None) -> Machine:
+    """Interleave the agents' programs: in every round each agent, in random order, runs until it
+    blocks, or for a random number of steps up to `max_burst` when that is set (finer interleavings).
+    `stalls` maps an agent to (program counter, rounds): the agent pauses that many rounds before that
+    operation - a warp that the hardware scheduler leaves waiting while the others run on."""
+    stalls = {a: list(v) for a, v in (stalls or {}).items()}
     m = Machine()
     m.barriers = {n: Barrier(n, c) for n, c in barriers.items()}
     pcs = {a: 0 for a in programs}
@@ -167,8 +190,16 @@ def run(programs: dict, barriers: dict, seed: int = 0, tma_bytes_to=None) -> Mac
         rng.shuffle(agents)
         for a in agents:
             prog = programs[a]
+            budget = rng.randint(1, max_burst) if max_burst else -1
             while pcs[a] < len(prog):
                 done = False
+                if budget == 0:
+                    break
+                budget -= 1
+                if a in stalls and stalls[a][0] == pcs[a] and stalls[a][1] > 0:
+                    stalls[a][1] -= 1
+                    progressed = True
+                    break
                 op = prog[pcs[a]]
                 kind = op[0]
                 if kind == "wait":
@@ -202,6 +233,36 @@ def run(programs: dict, barriers: dict, seed: int = 0, tma_bytes_to=None) -> Mac
                     m.barriers[op[1]].arrive(m.clock("umma"))
                 elif kind == "ld":
                     m.read(a, op[1], m.clock(a))
+                elif kind == "st":
+                    m.write(a, op[1], m.clock(a))
+                elif kind == "signal":
+                    m.tick(a)
+                    ctr = m.counters.setdefault(op[1], [0, Clock()])
+                    ctr[0] += 1
+                    ctr[1].join(m.clock(a))
+                elif kind == "wait_count":
+                    ctr = m.counters.setdefault(op[1], [0, Clock()])
+                    if ctr[0] < op[2]:
+                        break
+                    m.clock(a).join(ctr[1])
+                elif kind == "tma_load":
+                    # Every bulk copy is an asynchronous agent of its own: copies are ordered after the
+                    # thread that issued them, not after one another.
+                    _, cta, parts, buf, nbytes, bar = op
+                    agent = f"tma_load{cta}.{pcs[a]}"
+                    for part in parts:
+                        m.read(agent, part, m.clock(a))
+                    m.write(agent, buf, m.clock(a))
+                    m.barriers[bar].complete_tx(m.clock(agent), nbytes)
+                elif kind == "tma_store":
+                    _, cta, buf = op
+                    agent = f"tma_store{cta}.{pcs[a]}"
+                    m.read(agent, buf, m.clock(a))
+                    m.groups.setdefault(a, []).append(m.clock(agent).copy())
+                elif kind == "wait_read":
+                    groups = m.groups.get(a, [])
+                    for g in groups[:len(groups) - op[1]]:
+                        m.clock(a).join(g)
                 else:
                     raise ValueError(op)
                 pcs[a] += 1
@@ -219,7 +280,7 @@ def run(programs: dict, barriers: dict, seed: int = 0, tma_bytes_to=None) -> Mac
 
 # ---- the GEMM kernel's protocol ------------------------------------------------------
 def gemm_schedule(cta_group: int = 2, stages: int = 4, mh: int = 2, acc_bufs: int = 1, units=(8, 8, 8),
-                  stage_bytes: int = 48 * 1024, mutations=()):
+                  stage_bytes: int = 48 * 1024, mutations=(), push_chunks: int = 0):
     """Programs and barriers of gemm_tn_kernel for one cluster.
 
     `units` lists the k-block count of each work unit the cluster processes (0 =
@@ -231,6 +292,14 @@ def gemm_schedule(cta_group: int = 2, stages: int = 4, mh: int = 2, acc_bufs: in
       "expect_tx_short"            the leader announces one CTA's bytes instead of the group's
       "wrong_empty_parity"         the producer starts with the parity of a full ring
       "no_peer_commit"             the leader forgets to release the peer CTA's stages
+    With push_chunks > 0 every CTA also runs the pusher (that many chunks per tile):
+      "epilogue_signals_early"     a warp counts itself in before it has stored its part of the tile
+      "pusher_skips_tile_wait"     the pusher loads a tile without waiting for the warps' count
+      "pusher_skips_load_wait"     ... issues the stores without waiting for the load to land
+      "pusher_skips_read_wait"     ... refills a staging buffer that a store may still be reading
+      "pusher_wrong_parity"        ... waits on the load barrier with the parity of the other buffer's use
+      "shared_tile_counter"        the warps add to one shared count instead of publishing a slot each: a warp
+                                   that runs a tile ahead is then counted for one that has not stored yet
     """
     mut = set(mutations)
     ctas = range(cta_group)
@@ -250,6 +319,13 @@ def gemm_schedule(cta_group: int = 2, stages: int = 4, mh: int = 2, acc_bufs: in
         for w in range(8):
             programs[f"epilogue{c}.{w}"] = []
 
+    push_bytes = 16 * 1024
+    if push_chunks:
+        for c in ctas:
+            barriers[f"push{c}.0"] = 1
+            barriers[f"push{c}.1"] = 1
+            programs[f"pusher{c}"] = []
+    pushed = 0  # chunks pushed so far per CTA
     fill = 0   # ring slots filled so far (same sequence in every role)
     it = 0     # non-empty units so far
     for kbs in units:
@@ -288,6 +364,36 @@ def gemm_schedule(cta_group: int = 2, stages: int = 4, mh: int = 2, acc_bufs: in
                         e.append(("ld", f"tmem{c}.{buf}.{h}"))
                         if "epilogue_arrives_early" not in mut:
                             e.append(("arrive", f"tempty.{buf}.{h}"))
+                    if push_chunks:
+                        slot = f"stored{c}" if "shared_tile_counter" in mut else f"stored{c}.{w}"
+                        if "epilogue_signals_early" in mut:
+                            e.append(("signal", slot))
+                        e.append(("st", f"c{c}.{it}.{w}"))
+                        if "epilogue_signals_early" not in mut:
+                            e.append(("signal", slot))
+            if push_chunks:
+                # The load of a chunk is issued one iteration ahead of its stores, after the stores of
+                # the chunk before have read the buffer it fills (the kernel's loop, unrolled).
+                for c in ctas:
+                    p = programs[f"pusher{c}"]
+                    parts = [f"c{c}.{it}.{w}" for w in range(8)]
+                    for ch in range(push_chunks):
+                        g = pushed + ch
+                        if ch == 0 and "pusher_skips_tile_wait" not in mut:
+                            if "shared_tile_counter" in mut:
+                                p.append(("wait_count", f"stored{c}", 8 * (it + 1)))
+                            else:
+                                p.extend(("wait_count", f"stored{c}.{w}", it + 1) for w in range(8))
+                        if g > 0 and "pusher_skips_read_wait" not in mut:
+                            p.append(("wait_read", 1))
+                        p.append(("expect", f"push{c}.{g % 2}", push_bytes))
+                        p.append(("tma_load", c, parts, f"staging{c}.{g % 2}", push_bytes, f"push{c}.{g % 2}"))
+                        # (in the kernel the stores of chunk g - 1 are issued before this load; their
+                        # order against it is what wait_read establishes, so the program order here is equivalent)
+                        if "pusher_skips_load_wait" not in mut:
+                            p.append(("wait", f"push{c}.{g % 2}", g // 2 + (1 if "pusher_wrong_parity" in mut else 0)))
+                        p.append(("tma_store", c, f"staging{c}.{g % 2}"))
+                pushed += push_chunks
             it += 1
     return programs, barriers
 
@@ -297,3 +403,4 @@ def check_gemm(seeds=range(4), **kw) -> None:
     programs, barriers = gemm_schedule(**kw)
     for seed in seeds:
         run(programs, barriers, seed=seed)
+        run(programs, barriers, seed=seed, max_burst=3)

@@ -284,8 +284,10 @@ __global__ void __launch_bounds__(num_threads(BN, MH), 1)
     uint8_t *tail = smem_raw + (bars - raw) + 8u * (2 * C::STAGES + 9);
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(tail);
     volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(tail + 4);
-    volatile uint32_t *tiles_stored = reinterpret_cast<volatile uint32_t *>(tail + 8);  // epilogue warps x tiles
-    static_assert(8u * (2 * C::STAGES + 9) + 12u <= BAR_BYTES, "barrier area");
+    // tiles_stored[w]: how many tiles epilogue warp w has stored to C.  One slot per warp, not one shared
+    // count: a warp may run a tile or two ahead of another, and a sum could not tell whose parts are in.
+    volatile uint32_t *tiles_stored = reinterpret_cast<volatile uint32_t *>(tail + 8);
+    static_assert(8u * (2 * C::STAGES + 9) + 8u + 4u * 4 * EG <= BAR_BYTES, "barrier area");
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = CTA_GROUP == 1 ? 0u : ptx::cluster_ctarank();
@@ -310,7 +312,7 @@ __global__ void __launch_bounds__(num_threads(BN, MH), 1)
         ptx::mbar_init(push_bar(0), 1);
         ptx::mbar_init(push_bar(1), 1);
         *abort_flag = 0u;
-        *tiles_stored = 0u;
+        for (int w = 0; w < 4 * EG; w++) tiles_stored[w] = 0u;
         ptx::fence_mbar_init();
     }
     if (warp == 1) {
@@ -457,6 +459,7 @@ __global__ void __launch_bounds__(num_threads(BN, MH), 1)
         const bool plain = (p.alpha == 1.0f && p.beta == 0.0f);
         bool ok = true;
         int it = 0;
+        uint32_t tiles_done = 0;
         for (int t = cluster_id; t < num_units && ok; t += num_clusters) {
             const Unit u = unit_of(t, p, k_blocks);
             const TileCoord tc = tile_coord(u.tile, p);
@@ -517,10 +520,12 @@ __global__ void __launch_bounds__(num_threads(BN, MH), 1)
             }
             if (p.push) {
                 // This warp's part of the tile is in C: make the stores visible to the TMA unit
-                // (async proxy) and count the warp in for the pusher.
+                // (async proxy) and publish the warp's tile count for the pusher.
                 ptx::fence_proxy_async_global();
                 __syncwarp();
-                if (lane == 0) ptx::red_release_shared_add(ptx::smem_u32(const_cast<uint32_t *>(tiles_stored)), 1u);
+                tiles_done++;
+                if (lane == 0)
+                    ptx::st_release_shared(ptx::smem_u32(const_cast<uint32_t *>(tiles_stored + (warp - 2))), tiles_done);
             }
         }
     } else {
@@ -545,16 +550,18 @@ __global__ void __launch_bounds__(num_threads(BN, MH), 1)
             };
             // All epilogue warps have stored tile number `j` of this CTA.  false = gave up.
             auto tile_stored = [&](int j) -> bool {
-                const uint32_t want = uint32_t(j + 1) * uint32_t(4 * EG);
+                const uint32_t want = uint32_t(j + 1);
                 const uint64_t t0 = ptx::globaltimer_ns();
                 uint32_t spins = 0;
-                while (ptx::ld_acquire_shared(stored_addr) < want) {
-                    if ((++spins & 63u) == 0u) {
-                        if (*abort_flag) return false;
-                        if (ptx::globaltimer_ns() - t0 > wait_limit) {
-                            *abort_flag = 1u;
-                            report_timeout(p.status, WHERE_PUSHER, want, 0u);
-                            return false;
+                for (int w = 0; w < 4 * EG; w++) {
+                    while (ptx::ld_acquire_shared(stored_addr + 4u * uint32_t(w)) < want) {
+                        if ((++spins & 63u) == 0u) {
+                            if (*abort_flag) return false;
+                            if (ptx::globaltimer_ns() - t0 > wait_limit) {
+                                *abort_flag = 1u;
+                                report_timeout(p.status, WHERE_PUSHER, want, uint32_t(w));
+                                return false;
+                            }
                         }
                     }
                 }

@@ -92,8 +92,8 @@ __device__ __forceinline__ void st_global_v8(void *ptr, uint32_t a, uint32_t b, 
 // ---- TMA store from shared memory, and the flags around it ---------------------------------------------------
 // Order this thread's global-memory accesses (generic proxy) with those of the TMA unit (async proxy).
 __device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
-__device__ __forceinline__ void red_release_shared_add(uint32_t addr, uint32_t v) {
-    asm volatile("red.release.cta.shared::cta.add.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+__device__ __forceinline__ void st_release_shared(uint32_t addr, uint32_t v) {
+    asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
 }
 __device__ __forceinline__ uint32_t ld_acquire_shared(uint32_t addr) {
     uint32_t v;

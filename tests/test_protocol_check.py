@@ -35,3 +35,44 @@ def test_single_cta_mutations():
     for mutation in ("producer_skips_empty_wait", "mma_skips_tmem_wait", "epilogue_arrives_early"):
         with pytest.raises(ProtocolError):
             check_gemm(cta_group=1, stages=4, mh=1, acc_bufs=2, units=(6,) * 6, mutations=(mutation,))
+
+
+# ---- the pusher of the several-destination form ------------------------------------------
+@pytest.mark.parametrize("tiling", TILINGS)
+@pytest.mark.parametrize("units,chunks", [((8, 8, 8), 8), ((1,), 4), ((3, 5, 2, 7, 1), 2), ((4, 0, 4), 8), ((2,) * 7, 4)])
+def test_pusher_protocol_is_clean(tiling, units, chunks):
+    check_gemm(units=units, push_chunks=chunks, **tiling)
+
+
+@pytest.mark.parametrize("mutation,kind", [
+    ("epilogue_signals_early", "race"),                 # the TMA load reads a part of C that is still being stored
+    ("pusher_skips_tile_wait", ("race", "uninitialised")),
+    ("pusher_skips_load_wait", "race"),                 # the store reads the staging buffer while the load fills it
+    ("pusher_skips_read_wait", "race"),                 # the next load overwrites a buffer a store still reads
+    ("pusher_wrong_parity", ("parity", "deadlock")),
+])
+def test_pusher_bugs_are_reported(mutation, kind):
+    kinds = (kind,) if isinstance(kind, str) else kind
+    with pytest.raises(ProtocolError) as e:
+        check_gemm(cta_group=2, stages=4, mh=2, acc_bufs=1, units=(4, 4, 4, 4), push_chunks=4, mutations=(mutation,))
+    assert e.value.kind in kinds, str(e.value)
+
+
+def test_one_shared_tile_count_is_a_race_when_a_warp_falls_behind():
+    """The kernel publishes one tile count per epilogue warp.  With a single shared
+    count a warp that has handed its accumulator back but not yet stored its part
+    is covered by a faster warp's count for the next tile: the checker shows it
+    once that warp is held back, and shows the per-warp slots to be safe."""
+    from cute_rs_b200.check import gemm_schedule, run
+
+    def held_back(mutations):
+        programs, barriers = gemm_schedule(push_chunks=2, units=(2, 2, 2), mutations=mutations)
+        slow = "epilogue0.3"
+        pc = next(i for i, op in enumerate(programs[slow]) if op[0] == "st")
+        for seed in range(8):
+            run(programs, barriers, seed=seed, stalls={slow: (pc, 100)})
+
+    held_back(())
+    with pytest.raises(ProtocolError) as e:
+        held_back(("shared_tile_counter",))
+    assert e.value.kind in ("uninitialised", "race")
