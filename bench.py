@@ -37,8 +37,8 @@ METRIC = "bf16_gemm_tflops"
 UNIT = "TFLOP/s"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # DRAM bytes (read + write) of one 8192^3 bf16->bf16 launch of gemm_tn_kernel, from the
-# ncu capture summarised in profiles/gemm_tn_8192_bf16_ncu.md (831.0 MB + 120.3 MB).
-NCU_TRAFFIC_8192 = 951.3e6
+# ncu capture summarised in profiles/gemm_tn_8192_bf16_ncu.md (822.7 MB + 120.9 MB).
+NCU_TRAFFIC_8192 = 943.6e6
 
 
 def peaks():
