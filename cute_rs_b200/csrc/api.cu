@@ -369,10 +369,11 @@ static cute_b200_status workspace_get(int device, int slot, size_t bytes, void *
 
 // Streams and events of the host-buffer GEMM, created once per device.
 struct Pipeline {
-    static constexpr int kMaxPanels = 16;
+    static constexpr int kMaxPanels = 24;            // per operand
+    static constexpr int kMaxSteps = 2 * kMaxPanels;  // one upload per step
     bool ready = false;
     cudaStream_t up = nullptr, compute = nullptr, down = nullptr;
-    cudaEvent_t uploaded[kMaxPanels], computed[kMaxPanels], t0[kMaxPanels], t1[kMaxPanels];
+    cudaEvent_t uploaded[kMaxSteps], computed[kMaxSteps], t0[kMaxSteps], t1[kMaxSteps];
 };
 static Pipeline g_pipeline[kMaxDevices];
 
@@ -382,7 +383,7 @@ static cute_b200_status pipeline_get(int device, Pipeline **out) {
         CB_CUDA(cudaStreamCreateWithFlags(&p.up, cudaStreamNonBlocking));
         CB_CUDA(cudaStreamCreateWithFlags(&p.compute, cudaStreamNonBlocking));
         CB_CUDA(cudaStreamCreateWithFlags(&p.down, cudaStreamNonBlocking));
-        for (int i = 0; i < Pipeline::kMaxPanels; i++) {
+        for (int i = 0; i < Pipeline::kMaxSteps; i++) {
             CB_CUDA(cudaEventCreateWithFlags(&p.uploaded[i], cudaEventDisableTiming));
             CB_CUDA(cudaEventCreateWithFlags(&p.computed[i], cudaEventDisableTiming));
             CB_CUDA(cudaEventCreate(&p.t0[i]));
@@ -410,6 +411,30 @@ cute_b200_status cute_b200_release_workspace(void) {
     return CUTE_B200_OK;
 }
 
+// Cuts `dim` rows of `row_bytes` each into panels for the host-buffer GEMM: about eight of equal size (a
+// multiple of 256 rows, at least 2 MiB); with `tail` the end halves down to the smallest panel worth a
+// copy of its own (1 MiB, at least 256 rows).  row0[i] is the first row of panel i, row0[count] = dim.
+static int split_panels(int dim, size_t row_bytes, bool tail, int *row0) {
+    size_t min_rows = (((size_t(1) << 20) / (row_bytes ? row_bytes : 1) + 255) / 256) * 256;
+    if (min_rows < 256) min_rows = 256;
+    if (min_rows > size_t(dim)) min_rows = size_t(dim);
+    int big = ((dim / 8 + 255) / 256) * 256;
+    if (size_t(big) < 2 * min_rows) big = int(2 * min_rows);
+    int count = 0;
+    row0[0] = 0;
+    while (row0[count] < dim) {
+        const int left = dim - row0[count];
+        int take;
+        if (left > big + big / 2) take = big;
+        else if (tail && size_t(left) >= 2 * min_rows) take = ((left / 2 + 255) / 256) * 256;
+        else take = left;
+        if (count == Pipeline::kMaxPanels - 1) take = left;
+        row0[count + 1] = row0[count] + take;
+        count++;
+    }
+    return count;
+}
+
 cute_b200_status cute_b200_gemm_tn_host(const cute_b200_gemm_desc *desc, const void *hA, const void *hB, void *hC,
                                         double *seconds) {
     if (!desc) return fail(CUTE_B200_ERR_NULL_POINTER, "gemm_tn_host: desc is null");
@@ -426,48 +451,68 @@ cute_b200_status cute_b200_gemm_tn_host(const cute_b200_gemm_desc *desc, const v
     CB_TRY(workspace_get(device, 0, a_bytes ? a_bytes : 16, &dA));
     CB_TRY(workspace_get(device, 1, b_bytes ? b_bytes : 16, &dB));
     CB_TRY(workspace_get(device, 2, c_bytes, &dC));
-    // Three streams pipeline the call over row panels of A and C: while panel i
-    // is multiplied, panel i+1 is on its way up and panel i-1 on its way down
-    // (PCIe is full duplex).  B has to be whole on the device before the first
-    // panel can run.
+    // Three streams pipeline the call.  PCIe carries about 54 GB/s up or 57 GB/s down alone but only
+    // about 78 GB/s both ways together, so the way down has to start long before the way up ends: A and B
+    // go up alternately in panels of rows, and each new panel unlocks a block of C (its rows or columns
+    // against everything of the other operand that is already there), which is multiplied at once and
+    // sent down while the next panels come up.  The area of C that can be computed then grows as early
+    // as the data allows (with the product of the rows of A and B on the device).  The last uploads are
+    // small panels of A: what the last upload unlocks is the part that nothing hides, and rows of C
+    // come down as one contiguous copy, while a block of columns is a pitched copy that PCIe carries
+    // less well the narrower it is (52 against 57 GB/s at 2 KiB per row), so B has no small panels.
     Pipeline *pipe = nullptr;
     CB_TRY(pipeline_get(device, &pipe));
     const size_t c_elem = desc->c_dtype == CUTE_B200_BF16 ? 2 : 4;
     const bool reads_c = !(desc->alpha == 1.0f && desc->beta == 0.0f);
-    int panel_rows = ((desc->m / 8 + 511) / 512) * 512;
-    if (panel_rows < 1024) panel_rows = 1024;
-    int panels = (desc->m + panel_rows - 1) / panel_rows;
-    if (panels > Pipeline::kMaxPanels) {
-        panels = Pipeline::kMaxPanels;
-        panel_rows = (((desc->m + panels - 1) / panels + 511) / 512) * 512;
-        panels = (desc->m + panel_rows - 1) / panel_rows;
-    }
-    if (b_bytes) CB_CUDA(cudaMemcpyAsync(dB, hB, b_bytes, cudaMemcpyHostToDevice, pipe->up));
     cute_b200_status st = CUTE_B200_OK;
-    for (int i = 0; i < panels && st == CUTE_B200_OK; i++) {
-        const int row0 = i * panel_rows;
-        const int rows = desc->m - row0 < panel_rows ? desc->m - row0 : panel_rows;
-        const size_t a_off = size_t(row0) * desc->k * 2, c_off = size_t(row0) * desc->n * c_elem;
-        const size_t a_len = size_t(rows) * desc->k * 2, c_len = size_t(rows) * desc->n * c_elem;
-        if (a_len)
-            CB_CUDA(cudaMemcpyAsync(static_cast<char *>(dA) + a_off, static_cast<const char *>(hA) + a_off, a_len,
-                                    cudaMemcpyHostToDevice, pipe->up));
-        if (reads_c)
-            CB_CUDA(cudaMemcpyAsync(static_cast<char *>(dC) + c_off, static_cast<const char *>(hC) + c_off, c_len,
-                                    cudaMemcpyHostToDevice, pipe->up));
-        CB_CUDA(cudaEventRecord(pipe->uploaded[i], pipe->up));
-        CB_CUDA(cudaStreamWaitEvent(pipe->compute, pipe->uploaded[i], 0));
-        cute_b200_gemm_desc d = *desc;
-        d.m = rows;
-        if (seconds) CB_CUDA(cudaEventRecord(pipe->t0[i], pipe->compute));
-        st = gemm_tn(d, reinterpret_cast<uint64_t>(dA) + a_off, reinterpret_cast<uint64_t>(dB),
-                     reinterpret_cast<uint64_t>(dC) + c_off, pipe->compute, *dev);
-        if (st != CUTE_B200_OK) break;
-        if (seconds) CB_CUDA(cudaEventRecord(pipe->t1[i], pipe->compute));
-        CB_CUDA(cudaEventRecord(pipe->computed[i], pipe->compute));
-        CB_CUDA(cudaStreamWaitEvent(pipe->down, pipe->computed[i], 0));
-        CB_CUDA(cudaMemcpyAsync(static_cast<char *>(hC) + c_off, static_cast<char *>(dC) + c_off, c_len,
-                                cudaMemcpyDeviceToHost, pipe->down));
+    int steps = 0;
+    if (desc->k == 0) {
+        if (reads_c) CB_CUDA(cudaMemcpyAsync(dC, hC, c_bytes, cudaMemcpyHostToDevice, pipe->compute));
+        st = gemm_tn(*desc, 0, 0, reinterpret_cast<uint64_t>(dC), pipe->compute, *dev);
+        if (st == CUTE_B200_OK) CB_CUDA(cudaMemcpyAsync(hC, dC, c_bytes, cudaMemcpyDeviceToHost, pipe->compute));
+    } else {
+        int a_row0[Pipeline::kMaxPanels + 1], b_row0[Pipeline::kMaxPanels + 1];
+        const size_t row_bytes = size_t(desc->k) * 2, c_pitch = size_t(desc->n) * c_elem;
+        const int a_panels = split_panels(desc->m, row_bytes, true, a_row0);
+        const int b_panels = split_panels(desc->n, row_bytes, false, b_row0);
+        int ia = 0, ib = 0;  // panels of A and B on their way or on the device
+        while ((ia < a_panels || ib < b_panels) && st == CUTE_B200_OK) {
+            const bool is_a = ib >= b_panels || (ia < a_panels && a_row0[ia] <= b_row0[ib]);  // keep the rows level
+            // The panel going up, and the block of C it unlocks: rows [r0, r1) x columns [c0, c1).
+            int r0, r1, c0, c1;
+            if (is_a) {
+                r0 = a_row0[ia], r1 = a_row0[ia + 1], c0 = 0, c1 = b_row0[ib];
+                CB_CUDA(cudaMemcpyAsync(static_cast<char *>(dA) + r0 * row_bytes, static_cast<const char *>(hA) + r0 * row_bytes,
+                                        (r1 - r0) * row_bytes, cudaMemcpyHostToDevice, pipe->up));
+                ia++;
+            } else {
+                c0 = b_row0[ib], c1 = b_row0[ib + 1], r0 = 0, r1 = a_row0[ia];
+                CB_CUDA(cudaMemcpyAsync(static_cast<char *>(dB) + c0 * row_bytes, static_cast<const char *>(hB) + c0 * row_bytes,
+                                        (c1 - c0) * row_bytes, cudaMemcpyHostToDevice, pipe->up));
+                ib++;
+            }
+            if (r1 == r0 || c1 == c0) continue;  // nothing of the other operand is up yet
+            const size_t c_off = size_t(r0) * c_pitch + size_t(c0) * c_elem;
+            const size_t width = size_t(c1 - c0) * c_elem;
+            if (reads_c)
+                CB_CUDA(cudaMemcpy2DAsync(static_cast<char *>(dC) + c_off, c_pitch, static_cast<const char *>(hC) + c_off, c_pitch,
+                                          width, size_t(r1 - r0), cudaMemcpyHostToDevice, pipe->up));
+            const int i = steps++;
+            CB_CUDA(cudaEventRecord(pipe->uploaded[i], pipe->up));
+            CB_CUDA(cudaStreamWaitEvent(pipe->compute, pipe->uploaded[i], 0));
+            cute_b200_gemm_desc d = *desc;
+            d.m = r1 - r0;
+            d.n = c1 - c0;
+            if (seconds) CB_CUDA(cudaEventRecord(pipe->t0[i], pipe->compute));
+            st = gemm_tn_strided(d, reinterpret_cast<uint64_t>(dA) + r0 * row_bytes, reinterpret_cast<uint64_t>(dB) + c0 * row_bytes,
+                                 reinterpret_cast<uint64_t>(dC) + c_off, desc->n, pipe->compute, *dev);
+            if (st != CUTE_B200_OK) break;
+            if (seconds) CB_CUDA(cudaEventRecord(pipe->t1[i], pipe->compute));
+            CB_CUDA(cudaEventRecord(pipe->computed[i], pipe->compute));
+            CB_CUDA(cudaStreamWaitEvent(pipe->down, pipe->computed[i], 0));
+            CB_CUDA(cudaMemcpy2DAsync(static_cast<char *>(hC) + c_off, c_pitch, static_cast<char *>(dC) + c_off, c_pitch, width,
+                                      size_t(r1 - r0), cudaMemcpyDeviceToHost, pipe->down));
+        }
     }
     {
         const cute_b200_status sync = sync_and_check();  // waits for all three streams (device-wide)
@@ -475,7 +520,7 @@ cute_b200_status cute_b200_gemm_tn_host(const cute_b200_gemm_desc *desc, const v
     }
     if (seconds && st == CUTE_B200_OK) {
         double total = 0.0;
-        for (int i = 0; i < panels; i++) {
+        for (int i = 0; i < steps; i++) {
             float ms = 0.0f;
             if (cudaEventElapsedTime(&ms, pipe->t0[i], pipe->t1[i]) == cudaSuccess) total += double(ms) * 1e-3;
         }

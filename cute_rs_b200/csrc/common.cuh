@@ -52,6 +52,10 @@ cute_b200_status gemm_tn(const cute_b200_gemm_desc &desc, uint64_t a, uint64_t b
                          const DeviceState &dev);
 cute_b200_status gemm_tn_multi(const cute_b200_gemm_desc &desc, uint64_t a, uint64_t b, const uint64_t *c_list, int count,
                                cudaStream_t stream, const DeviceState &dev);
+// The same GEMM writing an m x n block of a wider row-major C: ldc elements between rows (>= n).
+// Never splits k (the second pass of a split assumes a dense C); k must be positive.
+cute_b200_status gemm_tn_strided(const cute_b200_gemm_desc &desc, uint64_t a, uint64_t b, uint64_t c, int ldc,
+                                 cudaStream_t stream, const DeviceState &dev);
 cute_b200_status gemm_tn_init(const DeviceState &dev);
 void gemm_tn_release_scratch();
 cute_b200_status gemm_tn_static(const cute_b200_gemm_desc &desc, uint64_t a, uint64_t b, uint64_t c, cudaStream_t stream,

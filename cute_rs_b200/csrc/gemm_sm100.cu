@@ -1014,9 +1014,14 @@ cute_b200_status gemm_tn_init(const DeviceState &) {
     return CUTE_B200_OK;
 }
 
-// Extra destinations of the next gemm_tn call on this thread (set by gemm_tn_multi).
-static thread_local const uint64_t *t_extra_c = nullptr;
-static thread_local int t_extra_count = 0;
+// What the plain entry point does not take: further destinations, a row pitch of C.
+struct GemmExtras {
+    const uint64_t *extra_c = nullptr;
+    int extra_count = 0;
+    int ldc = 0;  // 0 = n
+};
+static cute_b200_status gemm_tn_ex(const cute_b200_gemm_desc &d, uint64_t a, uint64_t b, uint64_t c, cudaStream_t stream,
+                                   const DeviceState &dev, const GemmExtras &ex);
 
 cute_b200_status gemm_tn_multi(const cute_b200_gemm_desc &d, uint64_t a, uint64_t b, const uint64_t *c_list, int count,
                                cudaStream_t stream, const DeviceState &dev) {
@@ -1040,16 +1045,30 @@ cute_b200_status gemm_tn_multi(const cute_b200_gemm_desc &d, uint64_t a, uint64_
     if (count > 1) {
         dd.split_k = 1;
     }
-    t_extra_c = c_list + 1;
-    t_extra_count = count - 1;
-    const cute_b200_status st = gemm_tn(dd, a, b, c_list[0], stream, dev);
-    t_extra_c = nullptr;
-    t_extra_count = 0;
-    return st;
+    GemmExtras ex;
+    ex.extra_c = c_list + 1;
+    ex.extra_count = count - 1;
+    return gemm_tn_ex(dd, a, b, c_list[0], stream, dev, ex);
 }
 
 cute_b200_status gemm_tn(const cute_b200_gemm_desc &d, uint64_t a, uint64_t b, uint64_t c, cudaStream_t stream,
                          const DeviceState &dev) {
+    return gemm_tn_ex(d, a, b, c, stream, dev, GemmExtras{});
+}
+
+cute_b200_status gemm_tn_strided(const cute_b200_gemm_desc &d, uint64_t a, uint64_t b, uint64_t c, int ldc,
+                                 cudaStream_t stream, const DeviceState &dev) {
+    if (ldc < d.n) return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "gemm_tn: row pitch %d of C is below n = %d", ldc, d.n);
+    if (d.k <= 0) return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "gemm_tn: a block of a wider C needs k > 0");
+    GemmExtras ex;
+    ex.ldc = ldc;
+    cute_b200_gemm_desc dd = d;
+    dd.split_k = 1;
+    return gemm_tn_ex(dd, a, b, c, stream, dev, ex);
+}
+
+static cute_b200_status gemm_tn_ex(const cute_b200_gemm_desc &d, uint64_t a, uint64_t b, uint64_t c, cudaStream_t stream,
+                                   const DeviceState &dev, const GemmExtras &ex) {
     if (d.m <= 0 || d.n <= 0 || d.k < 0)
         return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "gemm_tn: invalid size %dx%dx%d", d.m, d.n, d.k);
     if (d.ab_dtype != CUTE_B200_F16 && d.ab_dtype != CUTE_B200_BF16)
@@ -1092,7 +1111,8 @@ cute_b200_status gemm_tn(const cute_b200_gemm_desc &d, uint64_t a, uint64_t b, u
     p.M = d.m;
     p.N = d.n;
     p.K = d.k;
-    p.ldc = d.n;
+    const int ldc = ex.ldc ? ex.ldc : d.n;
+    p.ldc = ldc;
     p.alpha = d.alpha;
     p.beta = d.beta;
     p.status = dev.status_word;
@@ -1100,11 +1120,11 @@ cute_b200_status gemm_tn(const cute_b200_gemm_desc &d, uint64_t a, uint64_t b, u
     p.group_m = d.tuning[1];
     p.splits = splits;
     p.split_stride = 0;
-    p.extra_count = t_extra_count;
-    for (int i = 0; i < t_extra_count; i++) p.extra_c[i] = reinterpret_cast<void *>(t_extra_c[i]);
+    p.extra_count = ex.extra_count;
+    for (int i = 0; i < ex.extra_count; i++) p.extra_c[i] = reinterpret_cast<void *>(ex.extra_c[i]);
     const size_t c_elem = c_bf16 ? 2 : 4;
-    p.c_vec_ok = ((c & 15u) == 0 && (size_t(d.n) * c_elem) % 16 == 0) ? 1 : 0;
-    if ((c & 31u) == 0 && (size_t(d.n) * c_elem) % 32 == 0) p.c_vec_ok = 2;
+    p.c_vec_ok = ((c & 15u) == 0 && (size_t(ldc) * c_elem) % 16 == 0) ? 1 : 0;
+    if ((c & 31u) == 0 && (size_t(ldc) * c_elem) % 32 == 0) p.c_vec_ok = 2;
     const uint32_t fmt = d.ab_dtype == CUTE_B200_BF16 ? 1u : 0u;
     // Instruction descriptor: f32 accumulator, A and B format, both K-major,
     // N >> 3 at bit 17, M >> 4 at bit 24 (M counts the rows of the whole pair).
@@ -1116,7 +1136,8 @@ cute_b200_status gemm_tn(const cute_b200_gemm_desc &d, uint64_t a, uint64_t b, u
     // Several destinations: the pusher warp copies finished tiles by TMA when every C is 16-byte
     // aligned with a 16-byte row pitch; otherwise the epilogue stores to each of them from registers.
     CMaps tmC = {};
-    if (p.extra_count > 0 && splits == 1 && (c & 15u) == 0 && (size_t(d.n) * c_elem) % 16 == 0 && !(d.tuning[0] & 16)) {
+    if (p.extra_count > 0 && splits == 1 && ldc == d.n && (c & 15u) == 0 && (size_t(d.n) * c_elem) % 16 == 0 &&
+        !(d.tuning[0] & 16)) {
         const int box_rows = int(PUSH_BUF_BYTES) / (bn * int(c_elem));
         CB_TRY(make_tensor_map_c(&tmC.m[0], c, c_bf16, d.m, d.n, bn, box_rows));
         for (int i = 0; i < p.extra_count; i++)

@@ -406,10 +406,14 @@ def test_gemm_full_size_properties(lib, gpu):
 
 
 @pytest.mark.parametrize("m,n,k,cdt_name,alpha,beta", [(4096, 512, 256, "f32", 1.0, 0.0), (2600, 264, 136, "bf16", 1.0, 0.0),
-                                                        (3000, 128, 64, "f32", 1.5, -0.5), (100, 72, 0, "f32", 2.0, 0.5)])
+                                                        (3000, 128, 64, "f32", 1.5, -0.5), (100, 72, 0, "f32", 2.0, 0.5),
+                                                        (4096, 2304, 1024, "bf16", 1.0, 0.0), (3000, 1304, 1024, "f32", 1.5, -0.5),
+                                                        (520, 4104, 2048, "bf16", 2.0, 1.0)])
 def test_gemm_host_buffers_pipelined(lib, gpu, m, n, k, cdt_name, alpha, beta):
-    """cute_b200_gemm_tn_host: host buffers in and out, the call cut into row
-    panels that upload, multiply and download concurrently."""
+    """cute_b200_gemm_tn_host: host buffers in and out.  The larger cases are cut
+    into panels of A and B that go up alternately; every panel unlocks a block of
+    C that is multiplied (into a strided block of the device C) and comes down
+    while the next panels go up."""
     cdt = lib.F32 if cdt_name == "f32" else lib.BF16
     a, b, c = lcg_buffers([m * k, n * k, m * n], small=True)
     a_bits = oracle.f32_to_f16_bits(a.reshape(m, k))
