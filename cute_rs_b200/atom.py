@@ -290,6 +290,24 @@ class CopyOp:
             return self.rows * 64 * self.elem_bytes
 
     @dataclass(frozen=True)
+    class TmaStore:
+        """cp.async.bulk.tensor.2d.global.shared::cta.bulk_group of a (rows x cols
+        element) box of a row-major matrix from unswizzled shared memory; rows and
+        columns past the end of the matrix are clipped; completion by bulk group.
+        The pusher warp's copy of a finished tile into another GPU's C."""
+        rows: int
+        cols: int
+        elem_bytes: int = 2
+
+        @property
+        def box_bytes(self) -> int:
+            return self.rows * self.cols * self.elem_bytes
+
+        def __post_init__(self):
+            if self.cols > 256 or (self.cols * self.elem_bytes) % 16:
+                raise ValueError("TmaStore: at most 256 elements per box row, a multiple of 16 bytes")
+
+    @dataclass(frozen=True)
     class TmemLoad:
         """tcgen05.ld.32x32b.xN: a warp reads N consecutive 32-bit columns of its
         32 TMEM lanes; lane l of warp w addresses TMEM lane 32 * (w % 4) + l."""

@@ -118,3 +118,9 @@ def test_sm100_shared_memory_layout():
     assert sw128_descriptor(0x4400 + 32) - d == 2
     tma = CopyOp.TmaLoad(rows=256)
     assert tma.box_bytes == 32768 and CopyOp.TmaLoad(rows=128).box_bytes + tma.box_bytes == 48 * 1024  # one 512x256 stage
+    # the pusher's chunk: BN columns of whole tile rows, 16 KiB per staging buffer, for bf16 and f32 C
+    assert CopyOp.TmaStore(rows=32, cols=256, elem_bytes=2).box_bytes == 16384
+    assert CopyOp.TmaStore(rows=16, cols=256, elem_bytes=4).box_bytes == 16384
+    assert CopyOp.TmaStore(rows=64, cols=128, elem_bytes=2).box_bytes == 16384
+    with pytest.raises(ValueError):
+        CopyOp.TmaStore(rows=8, cols=260)
