@@ -32,3 +32,28 @@ def test_wait_that_runs_out_is_reported_and_the_device_stays_usable(lib, gpu, ct
     lib.gemm_tn(desc, dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), 0)
     lib.synchronize()
     assert np.array_equal(dC.cpu().numpy(), oracle.gemm_tn(a_bits, b_bits, oracle.F16))
+
+
+def test_pusher_gives_up_with_the_other_roles(lib, gpu):
+    """The several-destination form under the same knob: the pusher warp waits for
+    tiles that never come, sees the CTA give up, and returns with everything else;
+    afterwards the same call delivers C to every destination."""
+    import torch
+    m, n, k = 512, 512, 256
+    a, b, _ = lcg_buffers([m * k, n * k, 0], small=True)
+    a_bits, b_bits = oracle.f32_to_bf16_bits(a.reshape(m, k)), oracle.f32_to_bf16_bits(b.reshape(n, k))
+    dA = torch.from_numpy(a_bits.view(np.int16)).cuda()
+    dB = torch.from_numpy(b_bits.view(np.int16)).cuda()
+    dests = [torch.zeros(m, n, device="cuda") for _ in range(3)]
+    desc = lib.gemm_desc(m, n, k, lib.BF16, lib.F32)
+    desc.tuning[0] = 4 | 8
+    lib.gemm_tn_multi(desc, dA.data_ptr(), dB.data_ptr(), [t.data_ptr() for t in dests], 0)
+    with pytest.raises(lib.CuteB200Error) as e:
+        lib.synchronize()
+    assert e.value.status == lib.ERR_DEVICE_TIMEOUT
+    desc.tuning[0] = 0
+    lib.gemm_tn_multi(desc, dA.data_ptr(), dB.data_ptr(), [t.data_ptr() for t in dests], 0)
+    lib.synchronize()
+    want = oracle.gemm_tn(a_bits, b_bits, oracle.BF16)
+    for t in dests:
+        assert np.array_equal(t.cpu().numpy(), want)
