@@ -379,6 +379,42 @@ def test_runtime_gemm_bf16_normal_inputs(lib, gpu, m, n, k):
         assert (diff <= tensor_core_bound(k, mag) + bf16_ulp(acc)).all()
 
 
+@pytest.mark.parametrize("rank", [0, 5])
+def test_row_sharded_gemm_config_on_one_gpu(lib, gpu, rank):
+    """The 8-GPU workload, 32768 x 32768 x 8192 bf16 with normal(0, 0.02) inputs, as one rank
+    of eight sees it (cute_b200_gemm_tn_shard: 4096 rows of A, all of B, its rows of a full-size
+    C are not allocated here, so the shard goes to a C of its own).  Checked on bands of rows
+    against the oracle, and the two placements of C (own block / offset into a full C) agree."""
+    import torch
+    M = N = 32768
+    K = 8192
+    world = 8
+    begin, rows = lib.shard_rows(M, world, rank)
+    assert (begin, rows) == (rank * 4096, 4096)
+    g = torch.Generator(device="cuda").manual_seed(4 + rank)
+    A = (torch.randn(rows, K, device="cuda", generator=g) * 0.02).bfloat16()
+    B = (torch.randn(N, K, device="cuda", generator=g) * 0.02).bfloat16()
+    C = torch.empty(rows, N, device="cuda", dtype=torch.bfloat16)
+    desc = lib.gemm_desc(M, N, K, lib.BF16, lib.BF16)
+    lib.gemm_tn_shard(desc, world, rank, A.data_ptr(), B.data_ptr(), C.data_ptr(), False, 0)
+    torch.cuda.synchronize()
+    assert lib.device_status() == (0, 0, 0, 0)
+    # c_is_full: given the base of a full C the call writes at the rank's row offset; the base passed
+    # here is chosen so that those rows are exactly a second buffer (nothing else is touched)
+    C2 = torch.empty(rows, N, device="cuda", dtype=torch.bfloat16)
+    lib.gemm_tn_shard(desc, world, rank, A.data_ptr(), B.data_ptr(), C2.data_ptr() - begin * N * 2, True, 0)
+    torch.cuda.synchronize()
+    assert torch.equal(C.view(torch.int16), C2.view(torch.int16))
+    a_bits = A.view(torch.int16).cpu().numpy().view(np.uint16)
+    b_bits = B.view(torch.int16).cpu().numpy().view(np.uint16)
+    got = C.view(torch.int16).cpu().numpy().view(np.uint16)
+    for lo, hi in [(0, 32), (2048 - 16, 2048 + 16), (rows - 32, rows)]:
+        acc = oracle.gemm_tn(a_bits, b_bits, lib.BF16, rows=(lo, hi))[lo:hi]
+        mag = oracle.gemm_tn_abs(a_bits, b_bits, lib.BF16, rows=(lo, hi))[lo:hi]
+        diff = np.abs(oracle.bf16_bits_to_f32(got[lo:hi]).astype(np.float64) - acc.astype(np.float64))
+        assert (diff <= tensor_core_bound(K, mag) + bf16_ulp(acc)).all()
+
+
 def test_gemm_full_size_properties(lib, gpu):
     """8192^3 bf16: linearity in A (exact for a power-of-two scale) and
     agreement of the two tilings on sampled rows."""
