@@ -152,7 +152,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--skip-extras", action="store_true", help="skip cpu_baseline / e2e / secondary kernels (profiling runs)")
-    ap.add_argument("--only", choices=["add", "sgemm"], help="run just this secondary kernel (for ncu captures) and exit")
+    ap.add_argument("--only", choices=["add", "sgemm", "multi"],
+                    help="run just this secondary kernel (for ncu captures) and exit; multi = the several-destination GEMM "
+                         "with its copies of C on this one GPU")
     ap.add_argument("--log2n", type=int, default=28, help="--only add: log2 of the element count")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
@@ -176,7 +178,12 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     if args.only:
-        res = bench_add(lib, torch, peaks(), 1 << args.log2n) if args.only == "add" else bench_sgemm(lib, torch)
+        if args.only == "add":
+            res = bench_add(lib, torch, peaks(), 1 << args.log2n)
+        elif args.only == "sgemm":
+            res = bench_sgemm(lib, torch)
+        else:
+            res = bench_multi(lib, torch)
         print(json.dumps(res))
         return
 
@@ -339,11 +346,19 @@ def main():
                                      "(32 bytes per lane), 128 rows of C per CTA; closing barrier",
         }
         rep = {"unit": UNIT, "timing": "%d interleaved steps of each variant, CUDA events, max over ranks" % reps}
+        # What bounds a step that leaves all of C on every GPU: the slower of this GPU's share of the flops at the
+        # measured cuBLAS peak and the bytes it must send at the measured peer-copy rate (770 GB/s per direction).
+        t_flops = flop / world / (pk["bf16_tflops"] * 1e12) * 1e3
+        t_link = (world - 1) * rows * N * 2 / 770e9 * 1e3
+        rep["target"] = {"ms": max(t_flops, t_link), "flops_ms": t_flops, "nvlink_ms": t_link,
+                         "bound": "tensor" if t_flops >= t_link else "nvlink",
+                         "how": "max(2mnk / N / measured bf16 peak, (N-1)/N * bytes of C / 770 GB/s measured peer copy)"}
         for i, name in enumerate(variants):
             ms_v = float(sums[i].item())
             rep[name] = {"value": flop / (ms_v * 1e-3) / 1e12, "ms_per_step": ms_v, "how": how[name]}
             if name in equal:
                 rep[name]["equals_all_gather_result"] = equal[name]
+                rep[name]["frac_of_target"] = rep["target"]["ms"] / ms_v
         out["replicated"] = rep
         del full, full_nccl
         peer_c.close()
@@ -401,6 +416,35 @@ def bench_sgemm(lib, torch):
     ms = e0.elapsed_time(e1) / 10
     return {"workload": "sgemm_nt f32 4096^3 column-major, alpha 1.5, beta 0.5", "tflops": 2.0 * n ** 3 / ms / 1e9, "ms": ms,
             "bound": "fp32 FFMA pipe", "peak_nominal": 148 * 128 * 2 * 1.965e9 / 1e12}
+
+
+def bench_multi(lib, torch, copies=3):
+    """The GEMM that also delivers C to further destinations (the pusher warp), with all copies in
+    this GPU's own memory: what one rank of the replicated multi-GPU form runs, minus NVLink."""
+    n = 8192
+    g = torch.Generator(device="cuda").manual_seed(3)
+    A = (torch.randn(n, n, device="cuda", generator=g) * 0.02).bfloat16()
+    B = (torch.randn(n, n, device="cuda", generator=g) * 0.02).bfloat16()
+    dests = [torch.empty(n, n, device="cuda", dtype=torch.bfloat16) for _ in range(copies)]
+    ptrs = [t.data_ptr() for t in dests]
+    d = lib.gemm_desc(n, n, n, lib.BF16, lib.BF16)
+    s = torch.cuda.current_stream().cuda_stream
+    out = {"workload": f"bf16 8192^3 -> bf16, C written to {copies} buffers of this GPU"}
+    for label, fn in (("one_destination", lambda: lib.gemm_tn(d, A.data_ptr(), B.data_ptr(), ptrs[0], s)),
+                      ("pusher_warp", lambda: lib.gemm_tn_multi(d, A.data_ptr(), B.data_ptr(), ptrs, s))):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(10):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / 10
+        out[label] = {"ms": ms, "tflops": 2.0 * n ** 3 / ms / 1e9}
+    out["copies_equal"] = all(bool(torch.equal(dests[0], t)) for t in dests[1:])
+    return out
 
 
 def bench_ref_kernel(A, B, M, N, K, torch):
