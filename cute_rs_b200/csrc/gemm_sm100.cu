@@ -786,7 +786,7 @@ cute_b200_status set_smem_limit() {
 // pair tile is the reference point); used only to rank candidates.
 double tiling_efficiency(int group, int bn, int mh) {
     double e = 1.0;
-    if (group == 1) e *= (mh == 2 ? 0.90 : 0.86);
+    if (group == 1) e *= (mh == 2 ? 0.96 : 0.86);
     else if (mh == 1) e *= 0.92;
     if (bn == 128) e *= (mh == 2 ? 0.85 : 0.72);
     return e;
@@ -800,6 +800,10 @@ void choose_tiling(int m, int n, int k, int c_bytes, int sm_count, int want_grou
                    int want_splits, int *group, int *bn, int *mh, int *splits) {
     const double sm_rate = 1.0e13;       // dense 16-bit flop/s of one SM at the clocks a GEMM sustains
     const double unit_latency = 2.5e-6;  // fill the ring, drain the accumulator
+    // A launch of CTA pairs starts about 2 us later than one of single CTAs (cluster scheduling and the
+    // cluster barrier around the TMEM set-up); measured on one-wave problems: 1024^3 12.7 / 10.6 us,
+    // 2048^3 20.7 / 18.6, 3072^3 41.2 / 39.6 (pair / single), equal from 4096^3 on.
+    const double pair_start = 2.0e-6;
     const double hbm = 5.0e12;
     const int k_blocks = (k + BK - 1) / BK;
     double best = 1e300;
@@ -819,6 +823,7 @@ void choose_tiling(int m, int n, int k, int c_bytes, int sm_count, int want_grou
                     const double unit_time =
                         2.0 * rows * b * kb_per * BK / (g * sm_rate * tiling_efficiency(g, b, h)) + unit_latency;
                     double t = waves * unit_time;
+                    if (g == 2) t += pair_start;
                     if (s > 1) t += (double(s + 1) * m * n * 4 + double(m) * n * c_bytes) / hbm + 3e-6;
                     if (t < best) {
                         best = t;
