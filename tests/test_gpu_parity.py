@@ -268,6 +268,25 @@ def test_gemm_several_destinations(lib, gpu, m, n, k, cdt_name, cta_group, tile_
         assert np.all(got[m] == 7)
 
 
+@pytest.mark.parametrize("cdt_name", ["f32", "bf16"])
+def test_gemm_eight_destinations(lib, gpu, cdt_name):
+    """The largest fan-out the entry point takes (one own C and seven peers)."""
+    import torch
+    m, n, k = 1024, 768, 512
+    cdt = lib.F32 if cdt_name == "f32" else lib.BF16
+    a, b, _ = lcg_buffers([m * k, n * k, 0], small=True)
+    a_bits, b_bits = oracle.f32_to_bf16_bits(a.reshape(m, k)), oracle.f32_to_bf16_bits(b.reshape(n, k))
+    want = oracle.gemm_tn(a_bits, b_bits, lib.BF16, cdt)
+    np_c = np.float32 if cdt == lib.F32 else np.uint16
+    dests = [dev(np.full((m, n), 3, np_c)) for _ in range(8)]
+    dA, dB = dev(a_bits), dev(b_bits)
+    lib.gemm_tn_multi(lib.gemm_desc(m, n, k, lib.BF16, cdt), dA.data_ptr(), dB.data_ptr(), [t.data_ptr() for t in dests], 0)
+    torch.cuda.synchronize()
+    assert lib.device_status() == (0, 0, 0, 0)
+    for t in dests:
+        assert np.array_equal(host(t, np_c).reshape(m, n), want)
+
+
 def test_gemm_several_destinations_rejects_bad_arguments(lib, gpu):
     import torch
     c = torch.zeros(128 * 128 + 8, dtype=torch.float32, device="cuda")
