@@ -370,6 +370,7 @@ def main():
         out["sgemm"] = bench_sgemm(lib, torch)
         out["cpu_baseline"] = cpu_baseline(A, B, M, N, K)
         out["reference_gpu_kernel_restated"] = bench_ref_kernel(A, B, M, N, K, torch)
+        out["cublas_same_run"] = bench_cublas(A, B, args.steps, args.warmup, flop, step, torch)
 
     if rank == 0:
         print(json.dumps(out))
@@ -446,6 +447,36 @@ def bench_multi(lib, torch, copies=3):
         out[label] = {"ms": ms, "tflops": 2.0 * n ** 3 / ms / 1e9}
     out["copies_equal"] = all(bool(torch.equal(dests[0], t)) for t in dests[1:])
     return out
+
+
+def bench_cublas(A, B, steps, warmup, flop, step, torch):
+    """torch.matmul (cuBLAS) on the same operands, the same number of back-to-back launches, the
+    same GPU and process: a comparator beside the headline number, not part of it.  Long runs of
+    launches settle at the power cap, so the two are also timed in alternation (ten rounds of ten)."""
+    Bt = B.t()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def timed(fn, n):
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    mm = lambda: torch.matmul(A, Bt)
+    for _ in range(warmup):
+        mm()
+    torch.cuda.synchronize()
+    ms = timed(mm, steps)
+    ours, theirs = [], []
+    for _ in range(10):
+        ours.append(timed(step, 10))
+        theirs.append(timed(mm, 10))
+    mo, mt = statistics.median(ours), statistics.median(theirs)
+    return {"value": flop / (ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms, "steps": steps,
+            "alternating": {"this_library_ms": mo, "cublas_ms": mt, "ratio": mo / mt,
+                            "how": "medians of ten rounds of ten launches each, the two in turn"}}
 
 
 def bench_ref_kernel(A, B, M, N, K, torch):
