@@ -630,7 +630,7 @@ __global__ void __launch_bounds__(256) gemm_splitk_reduce(const float *__restric
     const bool plain = (alpha == 1.0f && beta == 0.0f);
     float acc[4];
     const int n = int(min(size_t(4), count - i4));
-    if (n == 4) {
+    if (n == 4 && (plane & 3) == 0) {  // planes 16 bytes apart in phase: else their float4 loads would be misaligned
         float4 a = *reinterpret_cast<const float4 *>(partial + i4);
         for (int s = 1; s < splits; s++) {
             const float4 b = *reinterpret_cast<const float4 *>(partial + s * plane + i4);

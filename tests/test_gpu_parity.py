@@ -304,6 +304,31 @@ def test_gemm_several_destinations_rejects_bad_arguments(lib, gpu):
     torch.cuda.synchronize()
 
 
+@pytest.mark.parametrize("seed", range(6))
+def test_gemm_random_shapes_and_tilings(lib, gpu, seed):
+    """A seeded sweep: ten problems per seed with random ragged sizes, input and output types,
+    tilings, k splits and epilogues, small-integer data, bit-exact against the oracle.  (With a k
+    split the partial sums are exact integers below 2^24, so the order of the sums cannot show.)"""
+    rng = np.random.default_rng(1000 + seed)
+    for _ in range(10):
+        m, n = int(rng.integers(1, 700)), int(rng.integers(1, 700))
+        k = 8 * int(rng.integers(1, 160))
+        ab = lib.F16 if rng.integers(2) else lib.BF16
+        cdt = lib.F32 if rng.integers(2) else lib.BF16
+        cta_group, tile_n, tile_m = int(rng.integers(0, 3)), int(rng.choice([0, 128, 256])), int(rng.choice([0, 128, 256]))
+        split_k = int(rng.choice([0, 1, 1, 2, 3, 5]))
+        alpha, beta = [(1.0, 0.0), (1.0, 0.0), (2.0, 0.0), (1.0, 1.0), (0.5, -1.0)][int(rng.integers(5))]
+        a = rng.integers(-4, 5, (m, k)).astype(np.float32)
+        b = rng.integers(-4, 5, (n, k)).astype(np.float32)
+        c0f = rng.integers(-8, 9, (m, n)).astype(np.float32)
+        a_bits, b_bits = conv(lib, ab)(a), conv(lib, ab)(b)
+        c0 = c0f if cdt == lib.F32 else oracle.f32_to_bf16_bits(c0f)
+        got = run_gemm(lib, a_bits, b_bits, ab, cdt, alpha, beta, c0=c0.copy(), tile_n=tile_n, cta_group=cta_group,
+                       tile_m=tile_m, split_k=split_k)
+        want = oracle.gemm_tn(a_bits, b_bits, ab, cdt, alpha, beta, c_init=c0)
+        assert np.array_equal(got, want), (m, n, k, ab, cdt, cta_group, tile_n, tile_m, split_k, alpha, beta)
+
+
 @pytest.mark.parametrize("cdt_name", ["f32", "bf16"])
 @pytest.mark.parametrize("alpha,beta", [(1.5, -0.5), (0.0, 1.0), (2.0, 0.0), (1.0, 1.0)])
 @pytest.mark.parametrize("tile_m", [128, 256])
@@ -318,7 +343,7 @@ def test_gemm_alpha_beta_epilogue(lib, gpu, cdt_name, alpha, beta, tile_m):
     assert np.array_equal(got, want)
 
 
-@pytest.mark.parametrize("m,n,k", [(256, 128, 512), (200, 136, 328), (512, 256, 1088), (128, 128, 64)])
+@pytest.mark.parametrize("m,n,k", [(256, 128, 512), (200, 136, 328), (512, 256, 1088), (128, 128, 64), (143, 365, 1080), (9, 7, 512)])
 @pytest.mark.parametrize("split_k", [2, 3, 5, 16])
 @pytest.mark.parametrize("cdt_name,alpha,beta", [("f32", 1.0, 0.0), ("bf16", 1.0, 0.0), ("f32", 1.5, -0.5), ("bf16", 2.0, 1.0)])
 def test_gemm_split_k(lib, gpu, m, n, k, split_k, cdt_name, alpha, beta):
