@@ -78,6 +78,29 @@ def test_elementwise_add_mixed_alignment_uses_scalar_kernel(lib, gpu):
     assert e.value.status == lib.ERR_MISALIGNED
 
 
+def test_elementwise_add_random_lengths_and_alignments(lib, gpu):
+    """A seeded sweep over lengths and independent 4-byte offsets of the three buffers: every
+    combination of the 256-bit, 128-bit and scalar kernels with ragged heads and tails."""
+    import torch
+    rng = np.random.default_rng(77)
+    big = 1 << 16
+    x = rng.uniform(-1, 1, big + 64).astype(np.float32)
+    y = rng.uniform(-1, 1, big + 64).astype(np.float32)
+    dx, dy = dev(x), dev(y)
+    for _ in range(40):
+        n = int(rng.choice([0, 1, 2, 7, 8, 9, 31, 33, 255, 2049, 4096, 5000, big]))
+        ox, oy, oo = (int(v) for v in rng.integers(0, 16, 3))
+        if rng.integers(2):
+            oy = ox + 8 * int(rng.integers(0, 2))  # often the same phase, so the vector kernels are reached
+            oo = ox + 4 * int(rng.integers(0, 3))
+        out = torch.full((big + 64,), 9.0, device="cuda")
+        lib.elementwise_add_f32(dx.data_ptr() + 4 * ox, dy.data_ptr() + 4 * oy, out.data_ptr() + 4 * oo, n, 0)
+        torch.cuda.synchronize()
+        want = np.full(big + 64, 9.0, np.float32)
+        want[oo:oo + n] = oracle.elementwise_add(x[ox:ox + n], y[oy:oy + n])
+        assert np.array_equal(out.cpu().numpy().view(np.uint32), want.view(np.uint32)), (n, ox, oy, oo)
+
+
 def test_elementwise_add_golden_and_lcg(lib, gpu, golden):
     import torch
     for small in (True, False):
@@ -507,6 +530,26 @@ def test_gemm_host_buffers_pipelined(lib, gpu, m, n, k, cdt_name, alpha, beta):
                                b_bits.ctypes.data if k else 0, hc.ctypes.data)
         assert np.array_equal(hc, want) and sec >= 0.0
     assert np.array_equal(a_bits, a_in) and np.array_equal(b_bits, b_in)  # inputs untouched
+    lib.release_workspace()
+
+
+def test_gemm_host_buffers_random_shapes(lib, gpu):
+    """Seeded ragged problems through the host-buffer call: sizes large enough for several panels of
+    A and B, so the blocks of C are strided pieces of the device C and come down as pitched copies."""
+    rng = np.random.default_rng(31)
+    for _ in range(6):
+        m, n = int(rng.integers(300, 2400)), int(rng.integers(300, 2400))
+        k = 8 * int(rng.integers(64, 300))
+        cdt = lib.F32 if rng.integers(2) else lib.BF16
+        alpha, beta = [(1.0, 0.0), (1.0, 0.0), (2.0, -1.0)][int(rng.integers(3))]
+        a_bits = oracle.f32_to_bf16_bits(rng.integers(-3, 4, (m, k)).astype(np.float32))
+        b_bits = oracle.f32_to_bf16_bits(rng.integers(-3, 4, (n, k)).astype(np.float32))
+        c0f = rng.integers(-8, 9, (m, n)).astype(np.float32)
+        c0 = c0f if cdt == lib.F32 else oracle.f32_to_bf16_bits(c0f)
+        want = oracle.gemm_tn(a_bits, b_bits, lib.BF16, cdt, alpha, beta, c_init=c0)
+        hc = c0.copy()
+        lib.gemm_tn_host(lib.gemm_desc(m, n, k, lib.BF16, cdt, alpha, beta), a_bits.ctypes.data, b_bits.ctypes.data, hc.ctypes.data)
+        assert np.array_equal(hc, want), (m, n, k, cdt, alpha, beta)
     lib.release_workspace()
 
 
