@@ -153,6 +153,21 @@ def test_sgemm_bit_exact(lib, gpu, m, n, k, small):
     assert np.array_equal(dC.cpu().numpy().view(np.uint32), want.view(np.uint32))
 
 
+def test_sgemm_random_shapes(lib, gpu):
+    """Seeded sweep over the shapes the kernel takes (multiples of 128 x 128 x 8) and epilogue scalars."""
+    import torch
+    rng = np.random.default_rng(9)
+    for _ in range(8):
+        m, n, k = 128 * int(rng.integers(1, 6)), 128 * int(rng.integers(1, 6)), 8 * int(rng.integers(0, 40))
+        alpha, beta = [(1.5, -0.5), (1.0, 0.0), (0.0, 1.0), (-2.0, 3.0)][int(rng.integers(4))]
+        a, b, c0 = (rng.uniform(-1, 1, s).astype(np.float32) for s in (max(m * k, 4), max(n * k, 4), m * n))
+        dA, dB, dC = dev(a), dev(b), dev(c0)
+        lib.sgemm_nt(m, n, k, alpha, beta, dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), 0)
+        torch.cuda.synchronize()
+        want = oracle.sgemm_nt(a[:m * k], b[:n * k], c0, alpha, beta, m, n, k)
+        assert np.array_equal(dC.cpu().numpy().view(np.uint32), want.view(np.uint32)), (m, n, k, alpha, beta)
+
+
 def test_sgemm_golden(lib, gpu, golden):
     import torch
     m, n, k = 256, 256, 64
@@ -308,6 +323,35 @@ def test_gemm_eight_destinations(lib, gpu, cdt_name):
     assert lib.device_status() == (0, 0, 0, 0)
     for t in dests:
         assert np.array_equal(host(t, np_c).reshape(m, n), want)
+
+
+@pytest.mark.parametrize("seed", range(3))
+def test_gemm_several_destinations_random(lib, gpu, seed):
+    """Seeded sweep of the several-destination form: ragged sizes, both output types, every tiling,
+    two to five copies; small-integer data, bit-exact, guard rows untouched."""
+    import torch
+    rng = np.random.default_rng(500 + seed)
+    for _ in range(8):
+        m, n = int(rng.integers(1, 900)), int(rng.integers(1, 900))
+        if rng.integers(3):
+            n = (n + 7) // 8 * 8  # mostly pitches the pusher can take; the rest go the register way
+        k = 8 * int(rng.integers(1, 120))
+        cdt = lib.F32 if rng.integers(2) else lib.BF16
+        cta_group, tile_n, tile_m = int(rng.integers(0, 3)), int(rng.choice([0, 128, 256])), int(rng.choice([0, 128, 256]))
+        copies = int(rng.integers(2, 6))
+        a_bits = oracle.f32_to_bf16_bits(rng.integers(-4, 5, (m, k)).astype(np.float32))
+        b_bits = oracle.f32_to_bf16_bits(rng.integers(-4, 5, (n, k)).astype(np.float32))
+        want = oracle.gemm_tn(a_bits, b_bits, lib.BF16, cdt)
+        np_c = np.float32 if cdt == lib.F32 else np.uint16
+        dests = [dev(np.full((m + 1, n), 7, np_c)) for _ in range(copies)]
+        dA, dB = dev(a_bits), dev(b_bits)
+        d = lib.gemm_desc(m, n, k, lib.BF16, cdt, 1.0, 0.0, tile_n, cta_group, tile_m, 0)
+        lib.gemm_tn_multi(d, dA.data_ptr(), dB.data_ptr(), [x.data_ptr() for x in dests], 0)
+        torch.cuda.synchronize()
+        assert lib.device_status() == (0, 0, 0, 0)
+        for x in dests:
+            got = host(x, np_c).reshape(m + 1, n)
+            assert np.array_equal(got[:m], want) and np.all(got[m] == 7), (m, n, k, cdt, cta_group, tile_n, tile_m, copies)
 
 
 def test_gemm_several_destinations_rejects_bad_arguments(lib, gpu):
