@@ -526,6 +526,44 @@ def test_row_sharded_gemm_config_on_one_gpu(lib, gpu, rank):
         assert (diff <= tensor_core_bound(K, mag) + bf16_ulp(acc)).all()
 
 
+def test_gemm_c_beyond_2_31_elements(lib, gpu):
+    """A C of 65536 x 33000 = 2.16e9 elements (the reference stops at 2^31: 32-bit element offsets):
+    rows at both ends and around the 2^31st element are checked against the oracle."""
+    import torch
+    m, n, k = 65536, 33000, 64
+    g = torch.Generator(device="cuda").manual_seed(11)
+    A = torch.randint(-3, 4, (m, k), device="cuda", generator=g).to(torch.bfloat16)
+    B = torch.randint(-3, 4, (n, k), device="cuda", generator=g).to(torch.bfloat16)
+    C = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+    lib.gemm_tn(lib.gemm_desc(m, n, k, lib.BF16, lib.BF16), A.data_ptr(), B.data_ptr(), C.data_ptr(), 0)
+    torch.cuda.synchronize()
+    assert lib.device_status() == (0, 0, 0, 0)
+    b_bits = B.view(torch.int16).cpu().numpy().view(np.uint16)
+    edge = (1 << 31) // n  # the row that holds element 2^31
+    for lo in (0, edge - 2, m - 4):
+        a_bits = A[lo:lo + 4].view(torch.int16).cpu().numpy().view(np.uint16)
+        want = oracle.gemm_tn(a_bits, b_bits, lib.BF16, lib.BF16)
+        got = C[lo:lo + 4].view(torch.int16).cpu().numpy().view(np.uint16)
+        assert np.array_equal(got, want), lo
+
+
+def test_elementwise_add_beyond_2_31_elements(lib, gpu):
+    """2^31 + 5 elements: 64-bit indexing in the kernel; the ends and the neighbourhood of 2^31 are compared."""
+    import torch
+    n = (1 << 31) + 5
+    x = torch.empty(n, device="cuda").uniform_(-1, 1)
+    y = torch.empty(n, device="cuda").uniform_(-1, 1)
+    out = torch.full((n + 3,), 2.0, device="cuda")
+    lib.elementwise_add_f32(x.data_ptr(), y.data_ptr(), out.data_ptr(), n, 0)
+    torch.cuda.synchronize()
+    for lo in (0, (1 << 31) - 4096, n - 4096):
+        want = oracle.elementwise_add(x[lo:lo + 4096].cpu().numpy(), y[lo:lo + 4096].cpu().numpy())
+        assert np.array_equal(out[lo:lo + 4096].cpu().numpy().view(np.uint32), want.view(np.uint32)), lo
+    assert bool((out[n:] == 2.0).all())
+    del x, y, out
+    torch.cuda.empty_cache()
+
+
 def test_gemm_full_size_properties(lib, gpu):
     """8192^3 bf16: linearity in A (exact for a power-of-two scale) and
     agreement of the two tilings on sampled rows."""
