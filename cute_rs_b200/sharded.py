@@ -45,6 +45,8 @@ class RowShardedGemm:
     def panels(self, count: int = 8):
         """Row panels of this rank's block as (first row within the block, rows):
         whole 128-row tiles, at most `count` of them."""
+        if self.rows == 0:
+            return []
         tiles = (self.rows + 127) // 128
         count = max(1, min(count, tiles))
         per = ((tiles + count - 1) // count) * 128
@@ -187,22 +189,29 @@ def launch_replicated_p2p(plan: RowShardedGemm, dA_shard: int, dB: int, peer_c: 
 
 def launch_replicated_fused(plan: RowShardedGemm, dA_shard: int, dB: int, peer_c: PeerBuffer, c_elem: int, group=None,
                             tile_m: int = 0, register_stores: bool = False) -> None:
-    """C replicated on every GPU by the GEMM kernel itself: one launch whose
-    epilogue warps store every finished tile into this rank's rows of its own C
-    and of every peer's C (peer mappings over NVLink), so the transfer rides
-    under the tensor-core work of the following tiles.  The stores are bulk
-    tensor (TMA) stores from a shared-memory staging buffer, one per destination
-    (``register_stores`` selects 32-byte stores straight from registers, which
-    NVLink carries less well).  No collective library is involved; the closing barrier only tells every rank that all peers' stores
-    into its C have completed."""
+    """C replicated on every GPU by the GEMM kernel itself: one launch that
+    stores every finished tile into this rank's rows of its own C and then
+    copies it, from inside the kernel, into the same rows of every peer's C
+    (peer mappings over NVLink): a pusher warp per CTA loads the tile back by TMA
+    (it is still in L2) and issues one bulk tensor store per peer while the
+    tensor cores work on the following tiles.  ``register_stores`` selects the
+    fallback instead, 32-byte stores to every destination straight from the
+    epilogue's registers, which NVLink carries far less well.  No collective
+    library is involved; the closing barrier only tells every rank that all
+    peers' stores into its C have completed.  The plan's epilogue must be the
+    plain one (alpha 1, beta 0).  A rank without rows (more ranks than 128-row
+    tiles) launches nothing and only joins the barrier."""
     import torch
     import torch.distributed as dist
     off = plan.row_begin * plan.n * c_elem
     dests = [peer_c.local + off] + [peer_c.ptrs[(plan.rank + s) % plan.world] + off for s in range(1, plan.world)]
-    d = _lib.gemm_desc(plan.rows, plan.n, plan.k, plan.desc.ab_dtype, plan.desc.c_dtype, tile_m=tile_m)
-    if register_stores:
-        d.tuning[0] |= 16
+    if not (plan.desc.alpha == 1.0 and plan.desc.beta == 0.0):
+        raise ValueError("launch_replicated_fused needs alpha = 1, beta = 0")
     stream = torch.cuda.current_stream()
-    _lib.gemm_tn_multi(d, dA_shard, dB, dests, stream.cuda_stream)
+    if plan.rows > 0:
+        d = _lib.gemm_desc(plan.rows, plan.n, plan.k, plan.desc.ab_dtype, plan.desc.c_dtype, tile_m=tile_m)
+        if register_stores:
+            d.tuning[0] |= 16
+        _lib.gemm_tn_multi(d, dA_shard, dB, dests, stream.cuda_stream)
     stream.synchronize()
     dist.barrier(group=group)

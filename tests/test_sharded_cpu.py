@@ -72,8 +72,16 @@ def _worker_overlap(rank, world, port, m, n, k, out_dir):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("m", [1024, 640])
+def test_panels_of_a_rank_without_rows():
+    from cute_rs_b200 import _lib
+    from cute_rs_b200.sharded import RowShardedGemm
+    assert RowShardedGemm(100, 96, 64, _lib.BF16, _lib.F32, 2, 1).panels(8) == []
+    assert RowShardedGemm(100, 96, 64, _lib.BF16, _lib.F32, 2, 0).panels(8) == [(0, 100)]
+    assert RowShardedGemm(1024, 96, 64, _lib.BF16, _lib.F32, 2, 1).panels(3) == [(0, 256), (256, 256)]
+
+
+@pytest.mark.parametrize("m", [1024, 640, 100])
 def test_two_ranks_replicate_with_overlapped_panels(tmp_path, m):
-    """Even split (1024): panel-by-panel exchange; ragged split (640): falls back to one gather."""
+    """Even split (1024): panel-by-panel exchange; ragged split (640) and a rank without rows (100): one gather."""
     mp.spawn(_worker_overlap, args=(2, _free_port(), m, 96, 64, str(tmp_path)), nprocs=2, join=True)
     assert all((tmp_path / f"ov{r}.npy").exists() for r in range(2))
