@@ -366,11 +366,19 @@ def main():
 
     # ---- secondary kernels and the CPU baseline: rank 0 of a 1-GPU run only ----------------
     if world == 1 and not args.skip_extras:
-        out["elementwise_add"] = bench_add(lib, torch, pk)
-        out["sgemm"] = bench_sgemm(lib, torch)
-        out["cpu_baseline"] = cpu_baseline(A, B, M, N, K)
-        out["reference_gpu_kernel_restated"] = bench_ref_kernel(A, B, M, N, K, torch)
-        out["cublas_same_run"] = bench_cublas(A, B, args.steps, args.warmup, flop, step, torch)
+        # The headline line must survive a failure of a side measurement: each one reports its own error.
+        extras = {
+            "elementwise_add": lambda: bench_add(lib, torch, pk),
+            "sgemm": lambda: bench_sgemm(lib, torch),
+            "cpu_baseline": lambda: cpu_baseline(A, B, M, N, K),
+            "reference_gpu_kernel_restated": lambda: bench_ref_kernel(A, B, M, N, K, torch),
+            "cublas_same_run": lambda: bench_cublas(A, B, args.steps, args.warmup, flop, step, torch),
+        }
+        for name, fn in extras.items():
+            try:
+                out[name] = fn()
+            except Exception as exc:  # noqa: BLE001 - reported in the line, never hidden
+                out[name] = {"error": f"{type(exc).__name__}: {exc}"}
 
     if rank == 0:
         print(json.dumps(out))
