@@ -6,7 +6,7 @@
 // a cp.async ring; nothing of their structure is kept.
 //
 // Structure (one persistent CTA, or CTA pair, per SM):
-//   warp 0   TMA producer: cp.async.bulk.tensor.2d loads of a (128 x 64) A
+//   warp 0   TMA producer: cp.async.bulk.tensor.2d loads of a (128 MH x 64) A
 //            block and a (BN/pair x 64) B block per stage into 128-byte
 //            swizzled shared memory, completion counted on the stage's `full`
 //            mbarrier.
@@ -17,16 +17,21 @@
 //   warps 2-9  epilogue: tcgen05.ld of the finished accumulator (each warp
 //            its own 32 TMEM lanes and every other 32-column chunk),
 //            alpha/beta, conversion, global stores.
+//   warp 10  pusher, only in the several-destination form (gemm_tn_multi): one
+//            thread copies every finished tile from C, still in L2, into the
+//            further copies of C (other GPUs' memory over NVLink) with a TMA
+//            load and one bulk tensor store per copy, behind the epilogue and
+//            beside the main loop of the following tiles.
 // Each CTA keeps one (MH = 1) or two (MH = 2) 128-row accumulators of BN f32
 // columns in TMEM.  When two sets fit in the 512 columns they are double
 // buffered and the epilogue of tile i overlaps the main loop of tile i+1; the
 // largest tile (256 rows x 256 columns per CTA) fills TMEM on its own, and the
 // next tile's MMAs restart half by half as the epilogue drains each half.
 //
-// With CTA_GROUP == 2 two CTAs of a cluster work on one 256-row tile: each
-// loads its own 128 rows of A and its own half of the B rows, the leader CTA
+// With CTA_GROUP == 2 two CTAs of a cluster work on one tile of 256 MH rows:
+// each loads its own rows of A and its own half of the B rows, the leader CTA
 // issues tcgen05.mma.cta_group::2 reading both shared memories, and each CTA
-// ends up with its 128 rows of the result in its own TMEM.  That halves the
+// ends up with its rows of the result in its own TMEM.  That halves the
 // B traffic per output.  Every CTA issues its own loads; none is shared.
 //
 // Every mbarrier wait has a time limit.  A waiter that gives up raises the
