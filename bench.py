@@ -65,7 +65,7 @@ class ClockSampler:
     """Samples SM clock and throttle reasons through NVML while a region runs."""
 
     def __init__(self, index: int):
-        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self.samples, self.power, self.reasons, self.max_mhz, self.power_limit = [], [], set(), None, None
         self._stop = threading.Event()
         self._thread = None
         try:
@@ -74,6 +74,10 @@ class ClockSampler:
             self.nv = pynvml
             self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
             self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            try:
+                self.power_limit = pynvml.nvmlDeviceGetEnforcedPowerLimit(self.h) / 1000.0
+            except Exception:
+                pass
         except Exception:
             self.nv = None
 
@@ -88,6 +92,10 @@ class ClockSampler:
         while not self._stop.is_set():
             try:
                 self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    self.power.append(nv.nvmlDeviceGetPowerUsage(self.h) / 1000.0)
+                except Exception:
+                    pass
                 mask = get(self.h)
                 for k, bit in names.items():
                     if mask & bit:
@@ -109,7 +117,8 @@ class ClockSampler:
 
     def summary(self):
         return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
-                "samples": len(self.samples), "reasons": sorted(self.reasons)}
+                "samples": len(self.samples), "reasons": sorted(self.reasons),
+                "power_w": max(self.power) if self.power else None, "power_limit_w": self.power_limit}
 
 
 def run_reference(args):
