@@ -464,56 +464,62 @@ cute_b200_status cute_b200_gemm_tn_host(const cute_b200_gemm_desc *desc, const v
     CB_TRY(pipeline_get(device, &pipe));
     const size_t c_elem = desc->c_dtype == CUTE_B200_BF16 ? 2 : 4;
     const bool reads_c = !(desc->alpha == 1.0f && desc->beta == 0.0f);
-    cute_b200_status st = CUTE_B200_OK;
     int steps = 0;
-    if (desc->k == 0) {
-        if (reads_c) CB_CUDA(cudaMemcpyAsync(dC, hC, c_bytes, cudaMemcpyHostToDevice, pipe->compute));
-        st = gemm_tn(*desc, 0, 0, reinterpret_cast<uint64_t>(dC), pipe->compute, *dev);
-        if (st == CUTE_B200_OK) CB_CUDA(cudaMemcpyAsync(hC, dC, c_bytes, cudaMemcpyDeviceToHost, pipe->compute));
-    } else {
-        int a_row0[Pipeline::kMaxPanels + 1], b_row0[Pipeline::kMaxPanels + 1];
-        const size_t row_bytes = size_t(desc->k) * 2, c_pitch = size_t(desc->n) * c_elem;
-        const int a_panels = split_panels(desc->m, row_bytes, true, a_row0);
-        const int b_panels = split_panels(desc->n, row_bytes, false, b_row0);
-        int ia = 0, ib = 0;  // panels of A and B on their way or on the device
-        while ((ia < a_panels || ib < b_panels) && st == CUTE_B200_OK) {
-            const bool is_a = ib >= b_panels || (ia < a_panels && a_row0[ia] <= b_row0[ib]);  // keep the rows level
-            // The panel going up, and the block of C it unlocks: rows [r0, r1) x columns [c0, c1).
-            int r0, r1, c0, c1;
-            if (is_a) {
-                r0 = a_row0[ia], r1 = a_row0[ia + 1], c0 = 0, c1 = b_row0[ib];
-                CB_CUDA(cudaMemcpyAsync(static_cast<char *>(dA) + r0 * row_bytes, static_cast<const char *>(hA) + r0 * row_bytes,
-                                        (r1 - r0) * row_bytes, cudaMemcpyHostToDevice, pipe->up));
-                ia++;
-            } else {
-                c0 = b_row0[ib], c1 = b_row0[ib + 1], r0 = 0, r1 = a_row0[ia];
-                CB_CUDA(cudaMemcpyAsync(static_cast<char *>(dB) + c0 * row_bytes, static_cast<const char *>(hB) + c0 * row_bytes,
-                                        (c1 - c0) * row_bytes, cudaMemcpyHostToDevice, pipe->up));
-                ib++;
+    // Everything that is queued below reads or writes the caller's buffers asynchronously, so whatever
+    // happens while queueing, the call only returns after the device-wide wait that follows.
+    auto issue = [&]() -> cute_b200_status {
+        cute_b200_status st = CUTE_B200_OK;
+        if (desc->k == 0) {
+            if (reads_c) CB_CUDA(cudaMemcpyAsync(dC, hC, c_bytes, cudaMemcpyHostToDevice, pipe->compute));
+            st = gemm_tn(*desc, 0, 0, reinterpret_cast<uint64_t>(dC), pipe->compute, *dev);
+            if (st == CUTE_B200_OK) CB_CUDA(cudaMemcpyAsync(hC, dC, c_bytes, cudaMemcpyDeviceToHost, pipe->compute));
+        } else {
+            int a_row0[Pipeline::kMaxPanels + 1], b_row0[Pipeline::kMaxPanels + 1];
+            const size_t row_bytes = size_t(desc->k) * 2, c_pitch = size_t(desc->n) * c_elem;
+            const int a_panels = split_panels(desc->m, row_bytes, true, a_row0);
+            const int b_panels = split_panels(desc->n, row_bytes, false, b_row0);
+            int ia = 0, ib = 0;  // panels of A and B on their way or on the device
+            while ((ia < a_panels || ib < b_panels) && st == CUTE_B200_OK) {
+                const bool is_a = ib >= b_panels || (ia < a_panels && a_row0[ia] <= b_row0[ib]);  // keep the rows level
+                // The panel going up, and the block of C it unlocks: rows [r0, r1) x columns [c0, c1).
+                int r0, r1, c0, c1;
+                if (is_a) {
+                    r0 = a_row0[ia], r1 = a_row0[ia + 1], c0 = 0, c1 = b_row0[ib];
+                    CB_CUDA(cudaMemcpyAsync(static_cast<char *>(dA) + r0 * row_bytes, static_cast<const char *>(hA) + r0 * row_bytes,
+                                            (r1 - r0) * row_bytes, cudaMemcpyHostToDevice, pipe->up));
+                    ia++;
+                } else {
+                    c0 = b_row0[ib], c1 = b_row0[ib + 1], r0 = 0, r1 = a_row0[ia];
+                    CB_CUDA(cudaMemcpyAsync(static_cast<char *>(dB) + c0 * row_bytes, static_cast<const char *>(hB) + c0 * row_bytes,
+                                            (c1 - c0) * row_bytes, cudaMemcpyHostToDevice, pipe->up));
+                    ib++;
+                }
+                if (r1 == r0 || c1 == c0) continue;  // nothing of the other operand is up yet
+                const size_t c_off = size_t(r0) * c_pitch + size_t(c0) * c_elem;
+                const size_t width = size_t(c1 - c0) * c_elem;
+                if (reads_c)
+                    CB_CUDA(cudaMemcpy2DAsync(static_cast<char *>(dC) + c_off, c_pitch, static_cast<const char *>(hC) + c_off, c_pitch,
+                                              width, size_t(r1 - r0), cudaMemcpyHostToDevice, pipe->up));
+                const int i = steps++;
+                CB_CUDA(cudaEventRecord(pipe->uploaded[i], pipe->up));
+                CB_CUDA(cudaStreamWaitEvent(pipe->compute, pipe->uploaded[i], 0));
+                cute_b200_gemm_desc d = *desc;
+                d.m = r1 - r0;
+                d.n = c1 - c0;
+                if (seconds) CB_CUDA(cudaEventRecord(pipe->t0[i], pipe->compute));
+                st = gemm_tn_strided(d, reinterpret_cast<uint64_t>(dA) + r0 * row_bytes, reinterpret_cast<uint64_t>(dB) + c0 * row_bytes,
+                                     reinterpret_cast<uint64_t>(dC) + c_off, desc->n, pipe->compute, *dev);
+                if (st != CUTE_B200_OK) break;
+                if (seconds) CB_CUDA(cudaEventRecord(pipe->t1[i], pipe->compute));
+                CB_CUDA(cudaEventRecord(pipe->computed[i], pipe->compute));
+                CB_CUDA(cudaStreamWaitEvent(pipe->down, pipe->computed[i], 0));
+                CB_CUDA(cudaMemcpy2DAsync(static_cast<char *>(hC) + c_off, c_pitch, static_cast<char *>(dC) + c_off, c_pitch, width,
+                                          size_t(r1 - r0), cudaMemcpyDeviceToHost, pipe->down));
             }
-            if (r1 == r0 || c1 == c0) continue;  // nothing of the other operand is up yet
-            const size_t c_off = size_t(r0) * c_pitch + size_t(c0) * c_elem;
-            const size_t width = size_t(c1 - c0) * c_elem;
-            if (reads_c)
-                CB_CUDA(cudaMemcpy2DAsync(static_cast<char *>(dC) + c_off, c_pitch, static_cast<const char *>(hC) + c_off, c_pitch,
-                                          width, size_t(r1 - r0), cudaMemcpyHostToDevice, pipe->up));
-            const int i = steps++;
-            CB_CUDA(cudaEventRecord(pipe->uploaded[i], pipe->up));
-            CB_CUDA(cudaStreamWaitEvent(pipe->compute, pipe->uploaded[i], 0));
-            cute_b200_gemm_desc d = *desc;
-            d.m = r1 - r0;
-            d.n = c1 - c0;
-            if (seconds) CB_CUDA(cudaEventRecord(pipe->t0[i], pipe->compute));
-            st = gemm_tn_strided(d, reinterpret_cast<uint64_t>(dA) + r0 * row_bytes, reinterpret_cast<uint64_t>(dB) + c0 * row_bytes,
-                                 reinterpret_cast<uint64_t>(dC) + c_off, desc->n, pipe->compute, *dev);
-            if (st != CUTE_B200_OK) break;
-            if (seconds) CB_CUDA(cudaEventRecord(pipe->t1[i], pipe->compute));
-            CB_CUDA(cudaEventRecord(pipe->computed[i], pipe->compute));
-            CB_CUDA(cudaStreamWaitEvent(pipe->down, pipe->computed[i], 0));
-            CB_CUDA(cudaMemcpy2DAsync(static_cast<char *>(hC) + c_off, c_pitch, static_cast<char *>(dC) + c_off, c_pitch, width,
-                                      size_t(r1 - r0), cudaMemcpyDeviceToHost, pipe->down));
         }
-    }
+        return st;
+    };
+    cute_b200_status st = issue();
     {
         const cute_b200_status sync = sync_and_check();  // waits for all three streams (device-wide)
         if (st == CUTE_B200_OK) st = sync;
