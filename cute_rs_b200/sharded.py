@@ -213,5 +213,9 @@ def launch_replicated_fused(plan: RowShardedGemm, dA_shard: int, dB: int, peer_c
         if register_stores:
             d.tuning[0] |= 16
         _lib.gemm_tn_multi(d, dA_shard, dB, dests, stream.cuda_stream)
+    # A one-element all-reduce queued behind the kernel is the barrier: it cannot finish on any rank
+    # before every rank has joined it, which each does only after its own pushes have completed.
+    # One wait for the stream then covers the kernel and the barrier.
+    token = torch.zeros(1, device="cuda")
+    dist.all_reduce(token, group=group)
     stream.synchronize()
-    dist.barrier(group=group)
