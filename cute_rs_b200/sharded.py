@@ -197,8 +197,9 @@ def launch_replicated_fused(plan: RowShardedGemm, dA_shard: int, dB: int, peer_c
     tensor cores work on the following tiles.  ``register_stores`` selects the
     fallback instead, 32-byte stores to every destination straight from the
     epilogue's registers, which NVLink carries far less well.  No collective
-    library is involved; the closing barrier only tells every rank that all
-    peers' stores into its C have completed.  The plan's epilogue must be the
+    library moves data; a one-element all-reduce queued behind the kernel is
+    the closing barrier that tells every rank that all peers' stores into its C
+    have completed.  The plan's epilogue must be the
     plain one (alpha 1, beta 0).  A rank without rows (more ranks than 128-row
     tiles) launches nothing and only joins the barrier."""
     import torch
