@@ -635,6 +635,29 @@ def test_gemm_host_buffers_random_shapes(lib, gpu):
     lib.release_workspace()
 
 
+def test_alloc_upload_copy_download_round_trip(lib, gpu):
+    """The memory entry points a multi-process caller builds on: allocate, upload, device-to-device copy,
+    export a handle, download, free; null and zero-size arguments answer with status codes."""
+    rng = np.random.default_rng(5)
+    src = rng.integers(0, 255, 1 << 20, dtype=np.uint8)
+    d0 = lib.upload(src.ctypes.data, src.nbytes)
+    d1 = lib.alloc(src.nbytes)
+    lib.copy_async(d1, d0, src.nbytes, 0)
+    lib.synchronize()
+    back = np.zeros_like(src)
+    lib.download(d1, back.ctypes.data, back.nbytes)
+    assert np.array_equal(back, src)
+    handle = lib.ipc_export(d1)
+    assert isinstance(handle, bytes) and len(handle) == 64 and any(handle)
+    lib.copy_async(d1, d0, 0, 0)  # nothing to copy is not an error
+    with pytest.raises(lib.CuteB200Error):
+        lib.copy_async(0, d0, 16, 0)
+    with pytest.raises(lib.CuteB200Error):
+        lib.ipc_export(0)
+    lib.free(d0)
+    lib.free(d1)
+
+
 # -------------------------------------------------------- launch by kernel name
 def test_launch_by_name_mirrors_the_reference_examples(lib, gpu, golden):
     from cute_rs_b200 import CudaContext, DeviceArg, DType
