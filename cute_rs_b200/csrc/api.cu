@@ -84,13 +84,40 @@ cute_b200_status current_device(DeviceState **out) {
     return CUTE_B200_OK;
 }
 
-// Read and clear the bounded-wait report of the current device.
+// Status word of `ordinal` if cute_b200_init has set that device up, else null.
+static uint32_t *status_word_if_ready(int ordinal) {
+    if (ordinal < 0 || ordinal >= kMaxDevices) return nullptr;
+    std::lock_guard<std::mutex> lock(g_device_mu);
+    return g_devices[ordinal].ready ? g_devices[ordinal].status_word : nullptr;
+}
+
+// Read and clear the bounded-wait report of the current device.  A device that
+// only cute_b200_gemm_tn_static has touched is not initialised here (that would
+// allocate): its report lives in the words that entry point owns.
 static cute_b200_status read_status(uint32_t out[4]) {
-    DeviceState *dev;
-    CB_TRY(current_device(&dev));
+    int ordinal = 0;
+    cudaError_t err = cudaGetDevice(&ordinal);
+    if (err != cudaSuccess) {
+        cudaGetLastError();
+        return fail(CUTE_B200_ERR_NO_DEVICE, "cudaGetDevice failed: %s", cudaGetErrorName(err));
+    }
+    uint32_t *word = status_word_if_ready(ordinal);
+    uint32_t *static_word = gemm_tn_static_status_words(ordinal);
+    if (!word && !static_word) {
+        DeviceState *dev;
+        CB_TRY(current_device(&dev));
+        word = dev->status_word;
+    }
     CB_CUDA(cudaDeviceSynchronize());
-    CB_CUDA(cudaMemcpy(out, dev->status_word, 16, cudaMemcpyDeviceToHost));
-    if (out[0] != 0) CB_CUDA(cudaMemset(dev->status_word, 0, 16));
+    out[0] = out[1] = out[2] = out[3] = 0;
+    if (word) {
+        CB_CUDA(cudaMemcpy(out, word, 16, cudaMemcpyDeviceToHost));
+        if (out[0] != 0) CB_CUDA(cudaMemset(word, 0, 16));
+    }
+    if (out[0] == 0 && static_word && static_word != word) {
+        CB_CUDA(cudaMemcpy(out, static_word, 16, cudaMemcpyDeviceToHost));
+        if (out[0] != 0) CB_CUDA(cudaMemset(static_word, 0, 16));
+    }
     return CUTE_B200_OK;
 }
 
@@ -546,13 +573,12 @@ cute_b200_status cute_b200_gemm_tn_multi(const cute_b200_gemm_desc *desc, uint64
 cute_b200_status cute_b200_gemm_tn_static(const cute_b200_gemm_desc *desc, uint64_t dA, uint64_t dB, uint64_t dC,
                                           void *stream) {
     if (!desc) return fail(CUTE_B200_ERR_NULL_POINTER, "gemm_tn_static: desc is null");
-    // A device already set up through cute_b200_init shares its status word, so
-    // a bounded-wait report shows up in cute_b200_synchronize as usual; otherwise
-    // the entry point uses status words of its own.  Nothing is initialised here.
+    // A device already set up through cute_b200_init shares its status word; otherwise
+    // the entry point uses status words of its own, which cute_b200_synchronize and
+    // cute_b200_device_status read as well.  Nothing is initialised here.
     int device = 0;
     uint32_t *shared = nullptr;
-    if (cudaGetDevice(&device) == cudaSuccess && device >= 0 && device < kMaxDevices && g_devices[device].ready)
-        shared = g_devices[device].status_word;
+    if (cudaGetDevice(&device) == cudaSuccess) shared = status_word_if_ready(device);
     return gemm_tn_static(*desc, dA, dB, dC, static_cast<cudaStream_t>(stream), shared);
 }
 

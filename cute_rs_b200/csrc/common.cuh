@@ -60,6 +60,8 @@ cute_b200_status gemm_tn_init(const DeviceState &dev);
 void gemm_tn_release_scratch();
 cute_b200_status gemm_tn_static(const cute_b200_gemm_desc &desc, uint64_t a, uint64_t b, uint64_t c, cudaStream_t stream,
                                 uint32_t *shared_status);
+// Device address of the status words gemm_tn_static owns on `device`, null until that entry point has run there.
+uint32_t *gemm_tn_static_status_words(int device);
 cute_b200_status sgemm_nt_init(const DeviceState &dev);
 
 }  // namespace cb

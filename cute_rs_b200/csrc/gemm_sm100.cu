@@ -801,8 +801,14 @@ double tiling_efficiency(int group, int bn, int mh) {
 // whole waves of work units (tile x k range) over the clusters that fit; a
 // unit costs its MMA time plus a fixed start/drain latency; a split GEMM also
 // pays a second pass over the f32 partial planes.
-void choose_tiling(int m, int n, int k, int c_bytes, int sm_count, int want_group, int want_bn, int want_mh,
-                   int want_splits, int *group, int *bn, int *mh, int *splits) {
+//
+// want_* != 0 fixes that choice.  A caller's want_splits > 1 is honoured as it
+// is (cut down to the number of k blocks and to max_splits), whether or not
+// the cost model would have picked it; with want_splits == 0 the splits
+// min_splits..max_splits compete, and a split above min_splits must leave each
+// range at least four k blocks.  Returns the estimate in seconds.
+double choose_tiling(int m, int n, int k, int c_bytes, int sm_count, int want_group, int want_bn, int want_mh,
+                     int want_splits, int min_splits, int max_splits, int *group, int *bn, int *mh, int *splits) {
     const double sm_rate = 1.0e13;       // dense 16-bit flop/s of one SM at the clocks a GEMM sustains
     const double unit_latency = 2.5e-6;  // fill the ring, drain the accumulator
     // A launch of CTA pairs starts about 2 us later than one of single CTAs (cluster scheduling and the
@@ -811,15 +817,22 @@ void choose_tiling(int m, int n, int k, int c_bytes, int sm_count, int want_grou
     const double pair_start = 2.0e-6;
     const double hbm = 5.0e12;
     const int k_blocks = (k + BK - 1) / BK;
+    if (max_splits > 16) max_splits = 16;
+    if (max_splits > k_blocks) max_splits = k_blocks;
+    if (max_splits < 1) max_splits = 1;
+    if (min_splits < 1) min_splits = 1;
+    if (min_splits > max_splits) min_splits = max_splits;
+    int s_lo = min_splits, s_hi = max_splits;
+    if (want_splits > 0) {
+        s_lo = s_hi = want_splits < min_splits ? min_splits : (want_splits > max_splits ? max_splits : want_splits);
+    }
     double best = 1e300;
     for (int g = 1; g <= 2; g++)
         for (int b = 128; b <= 256; b += 128)
             for (int h = 1; h <= 2; h++)
-                for (int s = 1; s <= 16; s++) {
-                    if ((want_group && g != want_group) || (want_bn && b != want_bn) || (want_mh && h != want_mh) ||
-                        (want_splits && s != want_splits))
-                        continue;
-                    if (s > 1 && (s > k_blocks / 4 || double(s) * m * n * 4 > 512e6)) continue;
+                for (int s = s_lo; s <= s_hi; s++) {
+                    if ((want_group && g != want_group) || (want_bn && b != want_bn) || (want_mh && h != want_mh)) continue;
+                    if (want_splits == 0 && s > min_splits && (s > k_blocks / 4 || double(s) * m * n * 4 > 512e6)) continue;
                     const long long rows = 128LL * g * h;
                     const long long units = ((m + rows - 1) / rows) * ((n + b - 1) / b) * s;
                     const long long clusters = sm_count / g;
@@ -835,29 +848,48 @@ void choose_tiling(int m, int n, int k, int c_bytes, int sm_count, int want_grou
                         *group = g, *bn = b, *mh = h, *splits = s;
                     }
                 }
+    return best;
 }
 
-// Grow-only scratch of the split-k path, one per device.
-void *g_scratch_ptr[64] = {};
-size_t g_scratch_size[64] = {};
+// Grow-only scratch of the split-k path, one per device, shared by every
+// stream.  `idle` is recorded behind the second pass of each split GEMM and the
+// next split GEMM's stream waits for it before its first pass, so two calls on
+// different streams take turns on the planes instead of racing.
+struct Scratch {
+    void *ptr = nullptr;
+    size_t size = 0;
+    cudaEvent_t idle = nullptr;
+};
+Scratch g_scratch[64];
 std::mutex g_scratch_mu;
 
-cute_b200_status scratch_get(size_t bytes, void **out) {
-    void **ptr = g_scratch_ptr;
-    size_t *size = g_scratch_size;
-    std::mutex &mu = g_scratch_mu;
+// Hands out the device's scratch (grown if needed) after making `stream` wait
+// for the previous user.  The caller queues its kernels and then calls
+// scratch_release on the same stream.
+cute_b200_status scratch_acquire(size_t bytes, cudaStream_t stream, void **out) {
     int device = 0;
     CB_CUDA(cudaGetDevice(&device));
     if (device < 0 || device >= 64) return fail(CUTE_B200_ERR_NO_DEVICE, "no current device");
-    std::lock_guard<std::mutex> lock(mu);
-    if (size[device] < bytes) {
-        if (ptr[device]) CB_CUDA(cudaFree(ptr[device]));
-        ptr[device] = nullptr;
-        size[device] = 0;
-        CB_CUDA(cudaMalloc(&ptr[device], bytes));
-        size[device] = bytes;
+    std::lock_guard<std::mutex> lock(g_scratch_mu);
+    Scratch &sc = g_scratch[device];
+    if (!sc.idle) CB_CUDA(cudaEventCreateWithFlags(&sc.idle, cudaEventDisableTiming));
+    if (sc.size < bytes) {
+        if (sc.ptr) CB_CUDA(cudaFree(sc.ptr));  // waits for the device: no user of the old planes is left
+        sc.ptr = nullptr;
+        sc.size = 0;
+        CB_CUDA(cudaMalloc(&sc.ptr, bytes));
+        sc.size = bytes;
     }
-    *out = ptr[device];
+    CB_CUDA(cudaStreamWaitEvent(stream, sc.idle, 0));  // an event never recorded counts as complete
+    *out = sc.ptr;
+    return CUTE_B200_OK;
+}
+
+cute_b200_status scratch_release(cudaStream_t stream) {
+    int device = 0;
+    CB_CUDA(cudaGetDevice(&device));
+    std::lock_guard<std::mutex> lock(g_scratch_mu);
+    CB_CUDA(cudaEventRecord(g_scratch[device].idle, stream));
     return CUTE_B200_OK;
 }
 
@@ -907,6 +939,12 @@ cute_b200_status static_setup(int device, StaticSetup **out) {
 }
 }  // namespace
 
+uint32_t *gemm_tn_static_status_words(int device) {
+    if (device < 0 || device >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    return g_static_setup[device].ready ? g_static_setup[device].status : nullptr;
+}
+
 cute_b200_status gemm_tn_static(const cute_b200_gemm_desc &d, uint64_t a, uint64_t b, uint64_t c, cudaStream_t stream,
                                 uint32_t *shared_status) {
     if (d.m <= 0 || d.n <= 0 || d.k <= 0)
@@ -942,35 +980,11 @@ cute_b200_status gemm_tn_static(const cute_b200_gemm_desc &d, uint64_t a, uint64
                     "gemm_tn_static: %d x %d with %d k ranges needs %zu bytes of scratch, the built-in buffer holds %zu",
                     d.m, d.n, d.split_k ? d.split_k : 2, plane * 4 * size_t(d.split_k ? d.split_k : 2), kStaticScratchBytes);
 
-    // Tiling as the allocating path would pick it, with the split limited to what
-    // the built-in buffer and k allow.
+    // The tiling comes from the same cost model as the allocating path, asked for at least
+    // two ranges and at most what the built-in array (and k) allow.
     int group = 2, bn = 256, mh = 2, splits = 2;
-    {
-        double best = 1e300;
-        for (int s = 2; s <= 16; s++) {
-            if (d.split_k && s != d.split_k) continue;
-            if (size_t(s) > max_splits_by_scratch || s > k_blocks) continue;
-            int g2 = 0, b2 = 0, h2 = 0, s2 = 0;
-            choose_tiling(d.m, d.n, d.k, c_bf16 ? 2 : 4, setup->sm_count, d.cta_group, d.tile_n, d.tile_m / 128, s, &g2, &b2,
-                          &h2, &s2);
-            if (s2 != s) continue;  // this split is not admissible for the shape
-            const long long rows = 128LL * g2 * h2;
-            const long long units = ((d.m + rows - 1) / rows) * ((d.n + b2 - 1) / b2) * s;
-            const long long clusters = setup->sm_count / g2;
-            const double t = double((units + clusters - 1) / clusters) *
-                                 (2.0 * rows * b2 * ((k_blocks + s - 1) / s) * BK / (g2 * 1.0e13 * tiling_efficiency(g2, b2, h2)) + 2.5e-6) +
-                             double(s + 1) * plane * 4 / 5.0e12;
-            if (t < best) best = t, group = g2, bn = b2, mh = h2, splits = s;
-        }
-        if (best == 1e300) {
-            // The cost model admits no split (k too short for it): take the caller's or the smallest.
-            splits = d.split_k ? d.split_k : 2;
-            if (splits > k_blocks) splits = k_blocks;
-            int s2 = 1;
-            choose_tiling(d.m, d.n, d.k, c_bf16 ? 2 : 4, setup->sm_count, d.cta_group, d.tile_n, d.tile_m / 128, 1, &group, &bn,
-                          &mh, &s2);
-        }
-    }
+    choose_tiling(d.m, d.n, d.k, c_bf16 ? 2 : 4, setup->sm_count, d.cta_group, d.tile_n, d.tile_m / 128, d.split_k, 2,
+                  int(max_splits_by_scratch < 16 ? max_splits_by_scratch : 16), &group, &bn, &mh, &splits);
 
     GemmParams p = {};
     p.C = setup->scratch;
@@ -981,6 +995,8 @@ cute_b200_status gemm_tn_static(const cute_b200_gemm_desc &d, uint64_t a, uint64
     p.alpha = 1.0f;
     p.beta = 0.0f;
     p.status = shared_status ? shared_status : setup->status;
+    p.debug = d.tuning[0] & (4 | 8);  // the two test knobs of the bounded waits; the measurement knobs stay off
+    p.group_m = d.tuning[1];
     p.splits = splits;
     p.split_stride = plane * 4;
     p.c_vec_ok = (size_t(d.n) * 4) % 32 == 0 ? 2 : ((size_t(d.n) * 4) % 16 == 0 ? 1 : 0);
@@ -1012,9 +1028,9 @@ void gemm_tn_release_scratch() {
     int device = 0;
     if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return;
     std::lock_guard<std::mutex> lock(g_scratch_mu);
-    if (g_scratch_ptr[device]) cudaFree(g_scratch_ptr[device]);
-    g_scratch_ptr[device] = nullptr;
-    g_scratch_size[device] = 0;
+    if (g_scratch[device].ptr) cudaFree(g_scratch[device].ptr);
+    g_scratch[device].ptr = nullptr;
+    g_scratch[device].size = 0;
 }
 
 cute_b200_status gemm_tn_init(const DeviceState &) {
@@ -1111,10 +1127,8 @@ static cute_b200_status gemm_tn_ex(const cute_b200_gemm_desc &d, uint64_t a, uin
     if (d.split_k < 0 || d.split_k > 16)
         return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "gemm_tn: split_k must be 0 (choose) to 16, got %d", d.split_k);
     int group = 2, bn = 256, mh = 2, splits = 1;
-    choose_tiling(d.m, d.n, d.k, c_bf16 ? 2 : 4, dev.sm_count, d.cta_group, d.tile_n, d.tile_m / 128, d.split_k, &group,
-                  &bn, &mh, &splits);
-    const int max_splits = ((d.k + BK - 1) / BK);
-    if (splits > max_splits) splits = max_splits;
+    choose_tiling(d.m, d.n, d.k, c_bf16 ? 2 : 4, dev.sm_count, d.cta_group, d.tile_n, d.tile_m / 128, d.split_k, 1, 16,
+                  &group, &bn, &mh, &splits);
 
     GemmParams p = {};
     p.C = reinterpret_cast<void *>(c);
@@ -1161,7 +1175,7 @@ static cute_b200_status gemm_tn_ex(const cute_b200_gemm_desc &d, uint64_t a, uin
         // epilogue.  The scratch is allocated on first need and kept.
         const size_t plane = size_t(d.m) * d.n;
         void *scratch = nullptr;
-        CB_TRY(scratch_get(plane * 4 * splits, &scratch));
+        CB_TRY(scratch_acquire(plane * 4 * splits, stream, &scratch));
         GemmParams q = p;
         q.C = scratch;
         q.alpha = 1.0f;
@@ -1183,7 +1197,7 @@ static cute_b200_status gemm_tn_ex(const cute_b200_gemm_desc &d, uint64_t a, uin
                                                                   p.C, d.alpha, d.beta);
         CB_CUDA(cudaGetLastError());
         count_launch();
-        return CUTE_B200_OK;
+        return scratch_release(stream);
     }
 #define CB_CASE(G, N_, H, BF) \
     if (group == G && bn == N_ && mh == H && c_bf16 == BF) return launch<G, N_, H, BF>(tmA, tmB, tmC, p, dev.sm_count, stream);

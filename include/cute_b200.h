@@ -79,7 +79,9 @@ cute_b200_status cute_b200_init(int32_t device_ordinal);
  * runtime_gemm::build (examples/runtime_gemm.rs:22-105).
  *
  * m, n >= 1; k >= 0 (k == 0 stores the beta term only); k must be a multiple
- * of 8 and A, B 16-byte aligned (TMA row pitch); C aligned to 16 bytes.
+ * of 8 and A, B 16-byte aligned (TMA row pitch); C needs only the alignment
+ * of its element type (16- or 32-byte alignment of its base and row pitch
+ * selects the wider stores).
  * The reference's own limits (multiples of 128 / 128 / 32) are enforced by
  * cute_b200_launch, which mirrors its launch checks. */
 typedef struct {
@@ -90,8 +92,12 @@ typedef struct {
     int32_t tile_n;    /* columns of C per tile: 0 = choose; 128 or 256 */
     int32_t cta_group; /* 0 = choose; 1 = one CTA per tile; 2 = a CTA pair shares each tile's MMAs */
     int32_t tile_m;    /* rows of C per CTA: 0 = choose; 128 or 256 */
-    int32_t split_k;   /* k ranges computed as separate work units and summed by a second kernel through an
-                          f32 scratch buffer the library allocates on first need: 0 = choose, 1 = never, <= 16 */
+    int32_t split_k;   /* k ranges computed as separate work units and summed in ascending order by a second kernel
+                          through an f32 scratch buffer the library allocates on first need: 0 = choose, 1 = never,
+                          2..16 = exactly that many (cut down to the number of 64-wide k blocks when k is shorter;
+                          ranges left without a block contribute zeros).  The scratch is one buffer per device shared
+                          by all streams: the library orders split launches on different streams one behind the
+                          other with an event, so they do not race, but they do not overlap either */
     int32_t tuning[2]; /* zero.  Measurement and test knobs: [0] bit 0 skips the loads, bit 1 the stores (results
                           are then meaningless), bits 2+3 make every in-kernel wait run out after 20 ms so that
                           the bounded-wait report can be tested, bit 4 makes cute_b200_gemm_tn_multi store to its
@@ -123,10 +129,12 @@ cute_b200_status cute_b200_release_workspace(void);
  * ordinary entry point is unsuitable as soon as the library decides to split
  * k, because that path creates its scratch buffer on first need.
  *
- * This variant computes the same result (same tilings, same k ranges added in
- * the same order, so the same bits as cute_b200_gemm_tn called with the same
- * split_k) but takes its scratch from a 32 MiB array that is part of the
- * library image.  Every GPU that loads the library holds those 32 MiB until
+ * This variant computes the same result (the tiling comes from the same cost
+ * model and the k ranges are added in the same order, so with the same
+ * split_k >= 2 it returns the same bits as cute_b200_gemm_tn; with split_k = 0
+ * the ordinary entry point may decide not to split at all, this one always
+ * uses at least two ranges) but takes its scratch from a 32 MiB array that is
+ * part of the library image.  Every GPU that loads the library holds those 32 MiB until
  * the process exits.  It calls no cudaMalloc, cudaFree or other allocating
  * routine, and it does not need cute_b200_init.
  *
@@ -134,7 +142,7 @@ cute_b200_status cute_b200_release_workspace(void);
  *   - limit: m * n * 4 bytes * split_k must fit in 32 MiB (33 554 432 bytes),
  *     e.g. 8192 x 128 in up to 8 ranges, 1024 x 1024 in up to 8; larger requests
  *     return CUTE_B200_ERR_INVALID_ARGUMENT with the sizes in the message.
- *     k must be positive and at least 128.
+ *     k must exceed 64 (two 64-wide k blocks are the least that can be split).
  *   - the first call on each device resolves the array's device address and
  *     raises the kernels' shared-memory limit (no allocation either); make that
  *     first call before any stream capture begins.
@@ -144,8 +152,9 @@ cute_b200_status cute_b200_release_workspace(void);
  *     (different streams, or concurrent host threads) race on it.  Serialise
  *     them on one stream or with events.
  *   - a bounded-wait report goes to the device's usual status word when the
- *     device was set up with cute_b200_init, else to words private to this
- *     entry point (first report wins and stays). */
+ *     device was set up with cute_b200_init, else to words owned by this entry
+ *     point; cute_b200_synchronize and cute_b200_device_status read (and
+ *     clear) either without allocating anything. */
 cute_b200_status cute_b200_gemm_tn_static(const cute_b200_gemm_desc *desc, uint64_t dA, uint64_t dB, uint64_t dC,
                                           void *stream);
 

@@ -194,9 +194,10 @@ def test_sgemm_rejects_bad_shapes(lib, gpu):
     assert e.value.status == lib.ERR_INVALID_ARGUMENT and "multiple of the tile size" in e.value.message
 
 
-def test_sgemm_full_size_sampled(lib, gpu):
-    """4096^3 (the sgemm config): full-size run, outputs sampled against the
-    oracle's single-element form."""
+def test_sgemm_full_size_bands(lib, gpu):
+    """4096^3 (the sgemm config): full-size run, checked bit for bit on whole bands
+    of 128 columns and of 128 rows (first, interior and last tiles), each band
+    computed by the oracle as a GEMM of its own, plus single elements elsewhere."""
     import torch
     n = 4096
     rng = np.random.default_rng(2)
@@ -205,7 +206,15 @@ def test_sgemm_full_size_sampled(lib, gpu):
     lib.sgemm_nt(n, n, n, 1.5, 0.5, dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), 0)
     torch.cuda.synchronize()
     got = dC.cpu().numpy()
-    for i, j in [(0, 0), (4095, 4095), (127, 128), (128, 127), (1000, 3001), (2048, 64), (63, 4032)]:
+    a2, b2, c2, g2 = a.reshape(n, n), b.reshape(n, n), c0.reshape(n, n), got.reshape(n, n)  # [l or j, i or j]
+    for j0 in (0, 1920, n - 128):  # columns j0 .. j0 + 128 of C: contiguous in column-major storage
+        want = oracle.sgemm_nt(a, np.ascontiguousarray(b2[:, j0:j0 + 128]), c2[j0:j0 + 128], 1.5, 0.5, n, 128, n)
+        assert np.array_equal(g2[j0:j0 + 128].reshape(-1).view(np.uint32), want.view(np.uint32)), j0
+    for i0 in (0, 2176, n - 128):  # rows i0 .. i0 + 128 of C
+        want = oracle.sgemm_nt(np.ascontiguousarray(a2[:, i0:i0 + 128]), b, np.ascontiguousarray(c2[:, i0:i0 + 128]), 1.5, 0.5,
+                               128, n, n)
+        assert np.array_equal(np.ascontiguousarray(g2[:, i0:i0 + 128]).reshape(-1).view(np.uint32), want.view(np.uint32)), i0
+    for i, j in [(127, 128), (128, 127), (1000, 3001), (2048, 64), (63, 4032)]:
         want = np.float32(oracle.sgemm_nt_naive_elem(a, b, float(c0[i + j * n]), 1.5, 0.5, n, n, n, i, j))
         assert got[i + j * n].view(np.uint32) == want.view(np.uint32), (i, j)
 
@@ -410,12 +419,17 @@ def test_gemm_alpha_beta_epilogue(lib, gpu, cdt_name, alpha, beta, tile_m):
     assert np.array_equal(got, want)
 
 
-@pytest.mark.parametrize("m,n,k", [(256, 128, 512), (200, 136, 328), (512, 256, 1088), (128, 128, 64), (143, 365, 1080), (9, 7, 512)])
-@pytest.mark.parametrize("split_k", [2, 3, 5, 16])
+@pytest.mark.parametrize("m,n,k", [(256, 128, 512), (200, 136, 328), (512, 256, 1088), (128, 128, 64), (143, 365, 1080), (9, 7, 512),
+                                   (256, 136, 1600)])
+@pytest.mark.parametrize("split_k", [2, 3, 5, 6, 16])
 @pytest.mark.parametrize("cdt_name,alpha,beta", [("f32", 1.0, 0.0), ("bf16", 1.0, 0.0), ("f32", 1.5, -0.5), ("bf16", 2.0, 1.0)])
 def test_gemm_split_k(lib, gpu, m, n, k, split_k, cdt_name, alpha, beta):
-    """k cut into ranges summed by the second kernel: exact on integer data,
-    including more ranges than k blocks (empty ranges contribute zeros)."""
+    """k cut into ranges summed by the second kernel: exact on integer data.  The
+    library takes the asked number of ranges as it is, cut down to the number of
+    64-wide k blocks (k = 64 therefore runs unsplit); where the blocks do not
+    divide evenly the last ranges stay empty and contribute zeros (k = 1600 in 6
+    ranges: 25 blocks, five ranges of five and an empty one; k = 328 in 5: six
+    blocks, three ranges of two and two empty ones)."""
     cdt = lib.F32 if cdt_name == "f32" else lib.BF16
     a, b, c = lcg_buffers([m * k, n * k, m * n], small=True)
     a_bits, b_bits = oracle.f32_to_f16_bits(a.reshape(m, k)), oracle.f32_to_f16_bits(b.reshape(n, k))
@@ -434,6 +448,32 @@ def test_gemm_split_k_random_within_bound(lib, gpu):
     for split_k in (0, 4, 8):  # 0: the library splits this shape on its own
         got = run_gemm(lib, a_bits, b_bits, lib.BF16, lib.F32, split_k=split_k)
         assert (np.abs(got.astype(np.float64) - want) <= allowed).all()
+
+
+def test_gemm_split_k_on_two_streams_takes_turns(lib, gpu):
+    """Split GEMMs share one scratch buffer per device.  Two of them queued on
+    different streams (a skinny shape the library splits by itself, and a forced
+    split of another size) must not mix their partial sums: the library orders
+    them with an event.  Integer data, so any mixing shows as wrong bits."""
+    import torch
+    shapes = [(8192, 128, 2048, 0), (1024, 256, 4096, 8)]
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    cases = []
+    for (m, n, k, split_k), seed in zip(shapes, (1, 2)):
+        rng = np.random.default_rng(seed)
+        a_bits = oracle.f32_to_bf16_bits(rng.integers(-8, 9, (m, k)).astype(np.float32))
+        b_bits = oracle.f32_to_bf16_bits(rng.integers(-8, 9, (n, k)).astype(np.float32))
+        cases.append((m, n, k, split_k, a_bits, b_bits, dev(a_bits.view(np.int16)), dev(b_bits.view(np.int16)),
+                      torch.zeros(m, n, device="cuda"), oracle.gemm_tn(a_bits, b_bits, oracle.BF16)))
+    torch.cuda.synchronize()
+    for _ in range(6):
+        for (m, n, k, split_k, _, _, dA, dB, dC, _), stream in zip(cases, streams):
+            lib.gemm_tn(lib.gemm_desc(m, n, k, lib.BF16, lib.F32, split_k=split_k), dA.data_ptr(), dB.data_ptr(), dC.data_ptr(),
+                        stream.cuda_stream)
+    torch.cuda.synchronize()
+    assert lib.device_status() == (0, 0, 0, 0)
+    for case in cases:
+        assert np.array_equal(case[8].cpu().numpy(), case[9])
 
 
 def test_gemm_k_zero_and_write_only_c(lib, gpu):
@@ -465,7 +505,8 @@ def test_gemm_rejects_bad_arguments(lib, gpu):
     assert e.value.status == lib.ERR_INVALID_ARGUMENT
 
 
-@pytest.mark.parametrize("m,n,k", [(1024, 1024, 1024), (2048, 2048, 2048), (8192, 128, 8192), (16384, 1024, 8192)])
+@pytest.mark.parametrize("m,n,k", [(1024, 1024, 1024), (2048, 2048, 2048), (4096, 4096, 4096), (8192, 8192, 8192),
+                                   (8192, 128, 8192), (16384, 1024, 8192)])
 def test_runtime_gemm_bf16_normal_inputs(lib, gpu, m, n, k):
     """The runtime_gemm sweep: bf16 in, bf16 out, normal(0, 0.02) seed 3.
     Large shapes are checked on a band of rows (the oracle computes only those)."""

@@ -60,6 +60,84 @@ def test_static_scratch_gemm_matches_the_allocating_one_twice_in_a_row(lib):
     got, ref, a_bits, b_bits, c0 = _both(lib, 8192, 128, 1024, 0, small=True, cdt=lib.F32)
     want = oracle.gemm_tn(a_bits, b_bits, oracle.BF16)
     assert np.array_equal(got, want) and np.array_equal(ref, want)
+    # five k blocks in four ranges: 2 + 2 + 1 and one range without a block, which must contribute zeros
+    # over whatever the calls above left in the array; random data, so the order of the additions counts
+    got, ref, a_bits, b_bits, c0 = _both(lib, 384, 256, 320, 4, small=False, cdt=lib.F32, alpha=0.75, beta=2.0)
+    assert np.array_equal(got, ref)
+
+
+def test_static_scratch_gemm_allocates_no_device_memory(lib):
+    """What the entry point exists for: with its inputs and output in place, a call
+    leaves the device's free memory exactly as it found it, and launches exactly two
+    kernels (the k ranges, then their sum)."""
+    import torch
+    torch.cuda.set_device(0)
+    m, n, k = 1024, 512, 2048
+    a, b, _ = lcg_buffers([m * k, n * k, 0], small=True)
+    dA, dB = _dev(oracle.f32_to_bf16_bits(a.reshape(m, k))), _dev(oracle.f32_to_bf16_bits(b.reshape(n, k)))
+    dC = torch.zeros(m, n, device="cuda")
+    desc = lib.gemm_desc(m, n, k, lib.BF16, lib.F32, split_k=4)
+    lib.gemm_tn_static(desc, dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), 0)  # first call on the device: set-up
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    launches_before = lib.launch_count()
+    lib.gemm_tn_static(desc, dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), 0)
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
+    assert lib.launch_count() - launches_before == 2
+    assert np.array_equal(dC.cpu().numpy(), oracle.gemm_tn(oracle.f32_to_bf16_bits(a.reshape(m, k)),
+                                                           oracle.f32_to_bf16_bits(b.reshape(n, k)), oracle.BF16))
+
+
+_NO_INIT_TIMEOUT = r"""
+import sys
+import numpy as np
+import torch
+sys.path.insert(0, sys.argv[1])
+from cute_rs_b200 import _lib as lib
+torch.cuda.set_device(0)
+m, n, k = 256, 256, 512
+dA = torch.ones(m, k, device="cuda", dtype=torch.bfloat16)
+dB = torch.ones(n, k, device="cuda", dtype=torch.bfloat16)
+dC = torch.zeros(m, n, device="cuda")
+desc = lib.gemm_desc(m, n, k, lib.BF16, lib.F32, split_k=2)
+lib.gemm_tn_static(desc, dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), 0)  # set-up call, cute_b200_init never runs
+torch.cuda.synchronize()
+free_before, _ = torch.cuda.mem_get_info()
+desc.tuning[0] = 4 | 8  # the producer withholds every load; waits give up after 20 ms
+lib.gemm_tn_static(desc, dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), 0)
+try:
+    lib.synchronize()
+    print("NO ERROR")
+except lib.CuteB200Error as e:
+    print("STATUS", e.status, e.message)
+print("FREE_UNCHANGED", torch.cuda.mem_get_info()[0] == free_before)
+print("CLEARED", lib.device_status())
+desc.tuning[0] = 0
+lib.gemm_tn_static(desc, dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), 0)
+lib.synchronize()
+print("RESULT_OK", bool((dC == float(k)).all()))
+"""
+
+
+def test_static_scratch_gemm_reports_a_timeout_without_init(lib):
+    """In a fresh process that never calls cute_b200_init, a bounded wait that runs
+    out inside the static entry point's kernel still reaches the host:
+    cute_b200_synchronize returns CUTE_B200_ERR_DEVICE_TIMEOUT (read from the words
+    the entry point owns, without allocating), the report is cleared, and the
+    next call computes the right result.  The wait is made to run out by the
+    test knob that keeps the producer from issuing anything; nothing faults."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, "-c", _NO_INIT_TIMEOUT, root], capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert f"STATUS {lib.ERR_DEVICE_TIMEOUT}" in out.stdout and "bounded wait gave up" in out.stdout, out.stdout
+    assert "FREE_UNCHANGED True" in out.stdout, out.stdout
+    assert "CLEARED (0, 0, 0, 0)" in out.stdout, out.stdout
+    assert "RESULT_OK True" in out.stdout, out.stdout
 
 
 def test_static_scratch_gemm_rejects_what_does_not_fit(lib):
