@@ -2,9 +2,11 @@
 src/layout/tests.rs) and the sm_100a atoms against the hand-written kernels."""
 import pytest
 
-from cute_rs_b200.atom import (CopyOp, Layout, MmaF16BF16Op, Sm100UmmaOp, UniversalFma, make_copy_atom, make_layout_tv,
-                               make_mma_atom, make_tiled_copy_a, make_tiled_copy_b, make_tiled_copy_tv, make_tiled_mma,
-                               sw128_descriptor, sw128_offset)
+from cute_rs_b200.atom import (CopyOp, Layout, MmaF16BF16Op, Sm100UmmaOp, UniversalFma, make_copy_atom, make_fragment,
+                               make_layout_tv, make_mma_atom, make_tiled_copy, make_tiled_copy_a, make_tiled_copy_b,
+                               make_tiled_copy_c, make_tiled_copy_c_atom, make_tiled_copy_d, make_tiled_copy_s,
+                               make_tiled_copy_tv, make_tiled_mma, sw128_descriptor, sw128_offset, TensorView, autovec_copy, copy,
+                               copy_if)
 from cute_rs_b200.host import DType
 
 
@@ -68,6 +70,105 @@ def test_tiled_copy_from_an_mma():
             assert ldsm.layout_src_tv_tiled(lane, v) == m + 16 * k
     ldsb = make_tiled_copy_b(make_copy_atom(DType.F16, CopyOp.LdMatrix(2)), mma)
     assert ldsb.tile_shape() == (8, 16) and ldsb.layout_src_tv_tiled(9, 3) == 1 + 8 * 11
+
+
+def test_tiled_copy_s_and_d_reuse_the_layouts_with_another_atom():
+    # tests/atoms.rs:47-52
+    mma = single_warp_mma()
+    ldsm = make_tiled_copy_a(make_copy_atom(DType.F16, CopyOp.LdMatrix(4)), mma)
+    s = make_tiled_copy_s(make_copy_atom(DType.F16, CopyOp.Universal(128)), ldsm)
+    d = make_tiled_copy_d(make_copy_atom(DType.F16, CopyOp.Universal(32)), ldsm)
+    a = mma.layout_a_tv()
+    for lane in range(32):
+        for v in range(8):
+            assert s.layout_tv_tiled(lane, v) == ldsm.layout_src_tv_tiled(lane, v)
+            assert d.layout_tv_tiled(lane, v) == a(lane + 32 * v)
+    assert s.tiler_mn() == ldsm.tiler_mn() == (16, 16) and s.atom.op == CopyOp.Universal(128)
+    c = make_tiled_copy_c(make_copy_atom(DType.F32, CopyOp.Universal(64)), mma)
+    assert (c.size(), c.tile_shape()) == (32, (16, 8))
+    assert all(c.layout_tv_tiled(t, v) == mma.layout_c_tv()(t + 32 * v) for t in range(32) for v in range(4))
+
+
+def test_tiled_copy_c_atom_is_the_smallest_c_copy():
+    # tests/atoms.rs:54-66: an m16n8 accumulator and a two-value atom: each thread keeps c0 and c1 (row g,
+    # columns 2t and 2t + 1), so the tile is rows 0..8 and all 8 columns, in the order (t, c0/c1)
+    c = make_tiled_copy_c_atom(make_copy_atom(DType.F32, CopyOp.Universal(64)), single_warp_mma())
+    assert c.layout_tv(((4, 8), 2)) == Layout(((4, 8), 2), ((8, 1), 32))
+    assert c.layout_tv() == Layout(((4, 8), 2), ((8, 1), 32))
+    assert c.tiler_mn() == (Layout(8, 1), Layout((4, 2), (2, 1)))
+    assert c.tile_shape() == (8, (4, 2))
+    # the values a thread keeps are its first accumulators: coordinates (lane / 4, 2 * (lane % 4) + v)
+    tm, tn = c.tiler_mn()
+    for lane in range(32):
+        for v in range(2):
+            idx = c.layout_tv_tiled(lane, v)
+            assert (tm(idx % 8), tn(idx // 8)) == (lane // 4, 2 * (lane % 4) + v)
+    with pytest.raises(ValueError, match="more than the 4 accumulators"):
+        make_tiled_copy_c_atom(make_copy_atom(DType.F32, CopyOp.Universal(256)), single_warp_mma())
+
+
+def test_retile_follows_the_copy_value_order():
+    # tests/atoms.rs:68-92
+    atom = make_copy_atom(DType.F16, CopyOp.LdMatrix(4))
+    # threads 8 x 4, each with a 4 x 2 block (columns fastest): copy value w is row w / 2, column w % 2
+    tiled = make_tiled_copy_tv(atom, Layout.row_major((8, 4)), Layout.row_major((4, 2)))
+    r = tiled.retile(make_fragment((2, 4)))
+    assert r.size() == 8 and r.values() == list(range(8))
+    # the same fragment stored row by row: value w is slot 4 * (w % 2) + w / 2
+    assert tiled.retile(Layout((2, 4), (4, 1))).values() == [0, 4, 1, 5, 2, 6, 3, 7]
+    # an MMA fragment retiled for the ldmatrix copy built from the same MMA keeps its value order and
+    # its (MMA_M, MMA_K) modes
+    ldsm = make_tiled_copy_a(atom, single_warp_mma())
+    view = ldsm.retile(make_fragment((8, 4, 2)))
+    assert view.rank() == 3 and (view.mode(1).size(), view.mode(2).size()) == (4, 2)
+    assert view.values() == list(range(64))
+
+
+def test_tiled_copy_misuse_is_rejected():
+    # tests/atoms.rs:94-108
+    atom = make_copy_atom(DType.F16, CopyOp.LdMatrix(4))
+    with pytest.raises(ValueError) as e:
+        make_tiled_copy_tv(atom, Layout.row_major((4, 4)), Layout.col_major(8))
+    assert "16 threads" in str(e.value) and "32 threads" in str(e.value)
+    with pytest.raises(ValueError, match="multiple of"):
+        make_tiled_copy_tv(atom, Layout.row_major((8, 4)), Layout.col_major(4))
+    with pytest.raises(ValueError, match="outside the 64-element tile"):
+        make_tiled_copy(make_copy_atom(DType.F32, CopyOp.Universal(32)), Layout((32, 4), (1, 32)), (8, 8))
+
+
+def test_copy_breaks_into_the_instructions_of_the_elementwise_example():
+    """examples/elementwise_add.rs:60-79: a thread's 4 x 4 values of a row-major (M, 512) tensor move as
+    four 128-bit accesses, one per row; copy_if consults the first flag of each; autovec_copy finds
+    the same width by itself and narrows it when the base is less aligned (src/atom/copy.rs:500-588)."""
+    n = 512
+    g = TensorView(Layout((4, 4), (1, n)), base_offset=3 * n + 8)
+    r = TensorView(Layout.col_major((4, 4)), register=True)
+    atom = make_copy_atom(DType.F32, CopyOp.Universal(128))
+    plan = copy(atom, g, r)
+    assert [(c.src, c.dst, c.values) for c in plan] == [(3 * n + 8 + i * n, 4 * i, 4) for i in range(4)]
+    flags = TensorView(Layout.col_major((4, 4)), register=True)
+    assert [c.pred for c in copy_if(atom, flags, g, r)] == [0, 4, 8, 12]
+    assert [(c.values, c.dst) for c in autovec_copy(DType.F32, r, g)] == [(4, 3 * n + 8 + i * n) for i in range(4)]
+    narrow = autovec_copy(DType.F32, r, TensorView(Layout((4, 4), (1, n)), base_offset=2))
+    assert len(narrow) == 8 and narrow[0].values == 2 and narrow[0].op == CopyOp.Universal(64)
+    with pytest.raises(ValueError, match="needs 4 contiguous source elements"):
+        copy(atom, TensorView(Layout((4, 4), (n, 1))), r)
+    with pytest.raises(ValueError, match="cannot prove that the source offset 2 is aligned to 4 elements"):
+        copy(atom, TensorView(Layout((4, 4), (1, n)), base_offset=2), r)
+    with pytest.raises(ValueError, match="is not a multiple of the atom's 4 values"):
+        copy(atom, TensorView(Layout((2, 4), (1, n))), TensorView(Layout.col_major((2, 4)), register=True))
+    with pytest.raises(ValueError, match="one flag per source element"):
+        copy_if(atom, TensorView(Layout(4, 1), register=True), g, r)
+
+
+def test_layout_recovered_from_values():
+    for l in (Layout((4, 8, 2), (8, 1, 32)), Layout((2, 4), (4, 1)), Layout(8, 3), Layout((2, 2, 2), (1, 16, 4))):
+        assert Layout.from_values(l.values()).values() == l.values()
+    assert Layout.from_values([0, 4, 1, 5, 2, 6, 3, 7]) == Layout((2, 4), (4, 1))
+    assert Layout(((4, 8), 2), ((0, 1), 0)).filter() == Layout(8, 1)
+    assert Layout(((4, 8), 2), ((2, 0), 1)).filter() == Layout((4, 2), (2, 1))
+    with pytest.raises(ValueError):
+        Layout.from_values([0, 1, 3, 4, 5])
 
 
 def test_tiled_mma_matches_the_restated_reference_kernel():
