@@ -14,9 +14,15 @@ N > 1  : (launched by torchrun, one rank per GPU) the row-sharded GEMM
 `value` is the whole-job TFLOP/s with operands resident in HBM, timed with
 CUDA events on the launching stream (max over ranks).  `e2e` is the same
 metric through the host-buffer C-ABI call with the host<->device copies inside
-the timed region.  `roofline` compares the dominant kernel with the measured
-cuBLAS bf16 peak of this pool; `cpu_baseline` times the CPU oracle on the host
-cores.  `--impl reference` times the reference's CPU arithmetic (the oracle:
+the timed region: cute_b200_gemm_tn_host on one GPU; on N > 1 the launcher for
+all the GPUs of the box, cute_b200_gemm_tn_sharded_host, which is one process
+driving every GPU - rank 0 makes that call while the other ranks wait on a
+host-side barrier with their GPUs idle.  `roofline` compares the dominant
+kernel with the measured cuBLAS bf16 throughput of the same kind of GPU;
+`cpu_baseline` times the CPU oracle on the host cores.  `parity` entries
+compare bands of rows of the results with the oracle (outside every timed
+region) under the reference's bound for tensor-core results plus one bf16 unit
+in the last place.  `--impl reference` times the reference's CPU arithmetic (the oracle:
 the reference itself is Rust and cannot be built in this image) on a bounded
 sample of the same workload.
 """
@@ -36,8 +42,9 @@ sys.path.insert(0, ROOT)
 METRIC = "bf16_gemm_tflops"
 UNIT = "TFLOP/s"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
-# DRAM bytes (read + write) of one 8192^3 bf16->bf16 launch of gemm_tn_kernel, from the
-# ncu capture summarised in profiles/gemm_tn_8192_bf16_ncu.md (822.7 MB + 120.9 MB).
+# DRAM bytes (read + write) of one 8192^3 bf16->bf16 launch of gemm_tn_kernel as one ncu capture
+# measured them (dram__bytes_read.sum 822.7 MB + dram__bytes_write.sum 120.9 MB): a constant taken
+# from that capture, not re-measured by this program.
 NCU_TRAFFIC_8192 = 943.6e6
 
 
@@ -59,6 +66,69 @@ def workload(n_gpus: int):
                     m=8192, n=8192, k=8192, seed=3)
     return dict(name="row-sharded bf16 GEMM 32768x32768x8192 (normal(0,0.02) seed 4, bf16 C, B replicated)",
                 m=32768, n=32768, k=8192, seed=4)
+
+
+def gen_b(torch, w, device="cuda"):
+    g = torch.Generator(device=device).manual_seed(w["seed"])
+    return (torch.randn(w["n"], w["k"], device=device, generator=g) * 0.02).bfloat16()  # the same on every rank
+
+
+def gen_a_rows(torch, w, rank, rows, device="cuda"):
+    """Rank `rank`'s rows of A: a stream of its own, so that any rank can rebuild any other's rows."""
+    g = torch.Generator(device=device).manual_seed(w["seed"] * 1000 + rank)
+    return (torch.randn(rows, w["k"], device=device, generator=g) * 0.02).bfloat16()
+
+
+class BandCheck:
+    """Oracle results for a few bands of rows of C = A B^T (bf16 in, bf16 out), computed once
+    and compared with any number of candidate results.  The bound is the reference's for
+    tensor-core results (tests/gpu.rs:146-176: 2 k 2^-23 sum|a b| per element) plus one bf16
+    unit in the last place for the final rounding.  The oracle is the checker only and runs
+    outside every timed region."""
+
+    def __init__(self, a_rows, b_bits, bands, k):
+        import numpy as np
+        import oracle
+        self.np, self.oracle, self.bands, self.k = np, oracle, bands, k
+        self.want, self.allowed = [], []
+        for lo, hi in bands:
+            acc = oracle.gemm_tn(a_rows, b_bits, oracle.BF16, rows=(lo, hi))[lo:hi]
+            mag = oracle.gemm_tn_abs(a_rows, b_bits, oracle.BF16, rows=(lo, hi))[lo:hi]
+            ulp = 2.0 ** (np.floor(np.log2(np.maximum(np.abs(acc.astype(np.float64)), 2.0 ** -126))) - 7)
+            self.want.append(acc.astype(np.float64))
+            self.allowed.append(2.0 * k * 2.0 ** -23 * mag.astype(np.float64) + ulp)
+
+    def check(self, c_rows_bits, row_offset=0):
+        """c_rows_bits: uint16 (rows, n) array holding (at least) the bands, whose row 0 is row `row_offset` of the block."""
+        np, worst, rows = self.np, -1.0, 0
+        for (lo, hi), want, allowed in zip(self.bands, self.want, self.allowed):
+            got = self.oracle.bf16_bits_to_f32(c_rows_bits[lo - row_offset:hi - row_offset]).astype(np.float64)
+            worst = max(worst, float((np.abs(got - want) - allowed).max()))
+            rows += hi - lo
+        return {"rows_checked": rows, "max_excess": worst, "ok": bool(worst <= 0.0)}
+
+
+def band_bits(torch, c, bands):
+    """The bands of a device (rows, n) bf16 tensor as one uint16 host array per band, stacked with their offsets kept."""
+    import numpy as np
+    lo0 = bands[0][0]
+    hi1 = bands[-1][1]
+    out = np.zeros((hi1 - lo0, c.shape[1]), np.uint16)
+    for lo, hi in bands:
+        out[lo - lo0:hi - lo0] = c[lo:hi].view(torch.int16).cpu().numpy().view(np.uint16)
+    return out, lo0
+
+
+def three_bands(rows, height=32):
+    if rows <= 3 * height:
+        return [(0, rows)]
+    mid = (rows // 2) // 8 * 8
+    return [(0, height), (mid, mid + height), (rows - height, rows)]
+
+
+def to_bits(torch, t):
+    import numpy as np
+    return t.view(torch.int16).cpu().numpy().view(np.uint16)
 
 
 class ClockSampler:
@@ -199,11 +269,12 @@ def main():
     w = workload(world)
     M, N, K = w["m"], w["n"], w["k"]
     row_begin, rows = lib.shard_rows(M, world, rank)
-    g = torch.Generator(device="cuda").manual_seed(w["seed"])
-    B = (torch.randn(N, K, device="cuda", generator=g) * 0.02).bfloat16()  # same on every rank
-    ga = torch.Generator(device="cuda").manual_seed(w["seed"] * 1000 + rank)
-    A = (torch.randn(rows, K, device="cuda", generator=ga) * 0.02).bfloat16()
+    B = gen_b(torch, w)
+    A = gen_a_rows(torch, w, rank, rows)
     C = torch.empty(rows, N, device="cuda", dtype=torch.bfloat16)
+    if world > 1:
+        os.environ.setdefault("GLOO_SOCKET_IFNAME", "lo")  # one node: the loopback interface always exists
+    host_group = dist.new_group(backend="gloo") if world > 1 else None  # barriers that leave the GPUs idle
     desc = lib.gemm_desc(M, N, K, lib.BF16, lib.BF16)
     stream = torch.cuda.current_stream().cuda_stream
 
@@ -255,9 +326,25 @@ def main():
            "config": {"workload": w["name"], "rows_per_gpu": rows, "l2": "operands (A+B+C >= 384 MB per GPU) exceed the 126 MB L2",
                       "timing": "cuda events on the launching stream, max over ranks"},
            "roofline": roofline, "clocks": clocks.summary(), "gpu_launches": int(launches)}
+    roofline["traffic_source"] = "one ncu capture of this kernel and shape, a constant of this program" if world == 1 else None
+
+    # ---- parity of the timed step's result: bands of this rank's rows against the oracle ----
+    if not args.skip_extras:
+        b_bits = to_bits(torch, B)
+        own = BandCheck(to_bits(torch, A), b_bits, three_bands(rows), K)
+        got, off = band_bits(torch, C, own.bands)
+        mine = own.check(got, off)
+        if world > 1:
+            gathered = [None] * world
+            dist.all_gather_object(gathered, mine, group=host_group)
+            out["parity"] = {"what": "the compute-only step: every rank checks three bands of its own rows of C against the oracle",
+                             "rows_checked": sum(x["rows_checked"] for x in gathered),
+                             "max_excess": max(x["max_excess"] for x in gathered), "ok": all(x["ok"] for x in gathered)}
+        else:
+            out["parity"] = dict(mine, what="three bands of rows of the timed step's C against the oracle")
 
     # ---- end to end through the host-buffer C-ABI call --------------------------------
-    if not args.skip_extras:
+    if not args.skip_extras and world == 1:
         hA = torch.empty(rows, K, dtype=torch.bfloat16).pin_memory()
         hB = torch.empty(N, K, dtype=torch.bfloat16).pin_memory()
         hC = torch.empty(rows, N, dtype=torch.bfloat16).pin_memory()
@@ -310,15 +397,22 @@ def main():
             "peer_copies": lambda: launch_replicated_p2p(plan, A.data_ptr(), B.data_ptr(), peer_c, 2, panels=8,
                                                          copy_streams=copy_streams),
             "fused_pusher_warp": lambda: launch_replicated_fused(plan, A.data_ptr(), B.data_ptr(), peer_c, 2),
+            "fused_pusher_warp_all_reduce_barrier": lambda: launch_replicated_fused(plan, A.data_ptr(), B.data_ptr(), peer_c, 2,
+                                                                                    barrier="all_reduce"),
             "fused_pusher_warp_tile_m_128": lambda: launch_replicated_fused(plan, A.data_ptr(), B.data_ptr(), peer_c, 2, tile_m=128),
             "fused_register_stores": lambda: launch_replicated_fused(plan, A.data_ptr(), B.data_ptr(), peer_c, 2, tile_m=128,
                                                                      register_stores=True),
         }
+        # The oracle's view of rows that a PEER computes and delivers into this rank's copy of C: the
+        # next rank's rows of A are rebuilt here from its seed.
+        peer = (rank + 1) % world
+        peer_begin, peer_rows = plan.spans[peer]
+        peer_check = BandCheck(to_bits(torch, gen_a_rows(torch, w, peer, peer_rows)), b_bits, three_bands(peer_rows), K)
         # correctness of each variant against the all-gather of the compute-only C
         step()
         ref_full = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
         dist.all_gather_into_tensor(ref_full, C)
-        equal = {}
+        equal, parity = {}, {}
         for name, fn in variants.items():
             if name == "compute_only":
                 continue
@@ -328,7 +422,15 @@ def main():
             fn()
             barrier()
             equal[name] = bool(torch.equal(dst, ref_full))
+            got, off = band_bits(torch, dst[row_begin:row_begin + rows], own.bands)
+            a_, b_ = own.check(got, off), None
+            got, off = band_bits(torch, dst[peer_begin:peer_begin + peer_rows], peer_check.bands)
+            b_ = peer_check.check(got, off)
+            parity[name] = {"rows_checked": a_["rows_checked"] + b_["rows_checked"], "max_excess": max(a_["max_excess"], b_["max_excess"]),
+                            "ok": a_["ok"] and b_["ok"]}
         del ref_full
+        all_parity = [None] * world
+        dist.all_gather_object(all_parity, parity, group=host_group)
         sums = torch.zeros(len(variants), device="cuda", dtype=torch.float64)
         for r in range(reps + 1):
             for i, fn in enumerate(variants.values()):
@@ -349,7 +451,11 @@ def main():
                            "(CUDA IPC mappings, copy engines, no NCCL) while the next is multiplied; closing barrier",
             "fused_pusher_warp": "one GEMM launch that also writes every finished tile into the peers' C over NVLink peer "
                                  "mappings: a pusher warp per CTA copies the tile by TMA (load from its own C in L2, bulk "
-                                 "tensor store to each peer) beside the next tiles' main loop; closing barrier",
+                                 "tensor store to each peer) beside the next tiles' main loop; the last CTA then adds 1 to this "
+                                 "rank's counter in every peer's memory and a one-thread kernel behind the GEMM waits (bounded) for "
+                                 "the peers' counters: no host synchronisation, no collective call",
+            "fused_pusher_warp_all_reduce_barrier": "the same kernel, closed by a one-element NCCL all-reduce queued behind it instead "
+                                                    "of the counters",
             "fused_pusher_warp_tile_m_128": "the same with 128 rows of C per CTA (double-buffered accumulators)",
             "fused_register_stores": "one GEMM launch whose epilogue warps store every chunk to the peers' C from registers "
                                      "(32 bytes per lane), 128 rows of C per CTA; closing barrier",
@@ -369,9 +475,31 @@ def main():
             if name in equal:
                 rep[name]["equals_all_gather_result"] = equal[name]
                 rep[name]["frac_of_target"] = rep["target"]["ms"] / ms_v
+                per_rank = [x[name] for x in all_parity]
+                rep[name]["parity"] = {"rows_checked": sum(x["rows_checked"] for x in per_rank),
+                                       "max_excess": max(x["max_excess"] for x in per_rank), "ok": all(x["ok"] for x in per_rank)}
+        rep["parity_what"] = ("every rank checks, against the oracle, three bands of its own rows and three bands of the rows the "
+                              "next rank computed and delivered into this rank's copy of C")
         out["replicated"] = rep
         del full, full_nccl
         peer_c.close()
+
+    # ---- N > 1: end to end and the one-call launcher, both through the C ABI from ONE process ------
+    # cute_b200_comm_create / cute_b200_gemm_tn_sharded[_host] drive all the GPUs from a single process
+    # (a host thread per GPU).  Rank 0 makes those calls; the other ranks have released their device
+    # memory and wait on a host-side (gloo) barrier, so nothing of theirs runs on any GPU meanwhile.
+    if world > 1 and not args.skip_extras:
+        del A, B, C
+        torch.cuda.empty_cache()
+        torch.cuda.synchronize()
+        dist.barrier(group=host_group)
+        if rank == 0:
+            try:
+                out.update(bench_launcher(lib, torch, w, world, pk, max(3, min(args.steps, 10))))
+            except Exception as exc:  # noqa: BLE001 - reported in the line, never hidden
+                out["e2e"] = {"error": f"{type(exc).__name__}: {exc}"}
+            torch.cuda.set_device(local_rank)
+        dist.barrier(group=host_group)
 
     # ---- secondary kernels and the CPU baseline: rank 0 of a 1-GPU run only ----------------
     if world == 1 and not args.skip_extras:
@@ -381,7 +509,8 @@ def main():
             "sgemm": lambda: bench_sgemm(lib, torch),
             "cpu_baseline": lambda: cpu_baseline(A, B, M, N, K),
             "reference_gpu_kernel_restated": lambda: bench_ref_kernel(A, B, M, N, K, torch),
-            "cublas_same_run": lambda: bench_cublas(A, B, args.steps, args.warmup, flop, step, torch),
+            "cublas_same_run": lambda: bench_cublas(A, B, args.steps, args.warmup, flop, step, torch, local_rank),
+            "strong_scaling_anchor": lambda: bench_anchor(lib, torch, pk),
         }
         for name, fn in extras.items():
             try:
@@ -393,6 +522,124 @@ def main():
         print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()
+
+
+def bench_launcher(lib, torch, w, world, pk, steps):
+    """Rank 0 only, every other rank idle: the whole 32768 x 32768 x 8192 GEMM through the launcher
+    that one process makes for all the GPUs.  `e2e`: whole matrices in pinned host memory in, C in
+    host memory out, every step (cute_b200_gemm_tn_sharded_host: each GPU uploads its rows of A and
+    its 1/N share of B, the shares travel on over NVLink, each GPU sends its rows of C back).
+    `c_abi_launcher`: the same GEMM on device buffers through cute_b200_gemm_tn_sharded, compute only
+    and with C replicated on every GPU (the fused form, and device-to-device copies for comparison),
+    wall-clock per call since the call returns when every GPU is done."""
+    import numpy as np
+    M, N, K = w["m"], w["n"], w["k"]
+    flop = 2.0 * M * N * K
+    comm = lib.comm_create(world)
+    res = {}
+    try:
+        info = lib.comm_info(comm)
+        spans = [lib.shard_rows(M, world, g) for g in range(world)]
+        hA = torch.empty(M, K, dtype=torch.bfloat16).pin_memory()
+        hB = torch.empty(N, K, dtype=torch.bfloat16).pin_memory()
+        hC = torch.empty(M, N, dtype=torch.bfloat16).pin_memory()
+        torch.cuda.set_device(0)
+        hB.copy_(gen_b(torch, w))
+        for g, (lo, rows) in enumerate(spans):
+            hA[lo:lo + rows].copy_(gen_a_rows(torch, w, g, rows))
+        torch.cuda.empty_cache()
+        desc = lib.gemm_desc(M, N, K, lib.BF16, lib.BF16)
+        for _ in range(2):
+            lib.gemm_tn_sharded_host(comm, desc, hA.data_ptr(), hB.data_ptr(), hC.data_ptr())
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            lib.gemm_tn_sharded_host(comm, desc, hA.data_ptr(), hB.data_ptr(), hC.data_ptr())  # returns with C on the host
+        checksum = float(hC[0, 0])  # the step's result is read on the host
+        dt = (time.perf_counter() - t0) / steps
+        # parity: bands of rows in the first, a middle and the last GPU's block, against the oracle
+        a_bits = hA.view(torch.int16).numpy().view(np.uint16)
+        b_bits = hB.view(torch.int16).numpy().view(np.uint16)
+        c_bits = hC.view(torch.int16).numpy().view(np.uint16)
+        bands = []
+        for g in sorted({0, world // 2, world - 1}):
+            lo, rows = spans[g]
+            bands += [(lo + 64, lo + 96), (lo + rows - 32, lo + rows)]
+        chk = BandCheck(a_bits, b_bits, bands, K)
+        par = chk.check(c_bits, 0)
+        res["e2e"] = {"value": flop / dt / 1e12, "unit": UNIT, "h2d_bytes_per_step": (M * K + N * K) * 2, "d2h_bytes_per_step": M * N * 2,
+                      "ms_per_step": dt * 1e3, "steps": steps,
+                      "api": "cute_b200_gemm_tn_sharded_host (one process, a host thread per GPU; pinned host buffers; synchronous); "
+                             "rank 0 calls it while the other ranks wait on a host-side barrier with their GPUs idle",
+                      "h2d_bytes_per_gpu": (spans[0][1] * K + N * K // world) * 2, "d2h_bytes_per_gpu": spans[0][1] * N * 2,
+                      "b_exchange": "each GPU uploads N/%d rows of B and passes them to the others by device-to-device copies over NVLink" % world,
+                      "checksum": checksum, "parity": par}
+        del hA, hB, hC, a_bits, b_bits, c_bits
+        # device buffers: one tensor per GPU, made by this process on each device
+        dA, dB, dC = [], [], []
+        for g, (lo, rows) in enumerate(spans):
+            torch.cuda.set_device(g)
+            dA.append(gen_a_rows(torch, w, g, rows, device=f"cuda:{g}"))
+            dB.append(gen_b(torch, w, device=f"cuda:{g}"))
+            dC.append(torch.empty(M, N, dtype=torch.bfloat16, device=f"cuda:{g}"))
+        torch.cuda.set_device(0)
+        ptr = lambda ts: [t.data_ptr() for t in ts]
+        blocks = [c[lo:lo + rows] for c, (lo, rows) in zip(dC, spans)]
+        modes = {"compute_only": (lib.REPLICATE_NONE, ptr(blocks)), "replicated_fused": (lib.REPLICATE_FUSED, ptr(dC)),
+                 "replicated_copies": (lib.REPLICATE_COPIES, ptr(dC))}
+        launcher = {"unit": UNIT, "api": "cute_b200_gemm_tn_sharded (one process; returns when every GPU is done)",
+                    "timing": "host clock around %d back-to-back calls, each of which waits for all GPUs" % steps,
+                    "peer_access": info["peer_access"]}
+        if not info["peer_access"]:
+            modes.pop("replicated_fused")
+        for name, (mode, cptrs) in modes.items():
+            for _ in range(2):
+                lib.gemm_tn_sharded(comm, desc, ptr(dA), ptr(dB), cptrs, mode)
+            t0 = time.perf_counter()
+            for _ in range(steps):
+                lib.gemm_tn_sharded(comm, desc, ptr(dA), ptr(dB), cptrs, mode)
+            ms = (time.perf_counter() - t0) / steps * 1e3
+            launcher[name] = {"value": flop / (ms * 1e-3) / 1e12, "ms_per_step": ms}
+            if mode != lib.REPLICATE_NONE:
+                # GPU 0's copy of C must hold the rows the LAST GPU computed
+                lo, rows = spans[world - 1]
+                a_last = to_bits(torch, dA[world - 1])
+                chk = BandCheck(a_last, to_bits(torch, dB[0]), three_bands(rows), K)
+                got, off = band_bits(torch, dC[0][lo:lo + rows], chk.bands)
+                launcher[name]["parity"] = chk.check(got, off)
+                dC[0].zero_()
+        res["c_abi_launcher"] = launcher
+        del dA, dB, dC, blocks
+    finally:
+        lib.comm_destroy(comm)
+    return res
+
+
+def bench_anchor(lib, torch, pk):
+    """The workload of the multi-GPU runs, 32768 x 32768 x 8192, on this one GPU (it fits: 3 GiB):
+    the same-workload base for the strong-scaling curve of `bench.py --gpus 2/4/8`."""
+    w = workload(2)
+    M, N, K = w["m"], w["n"], w["k"]
+    B = gen_b(torch, w)
+    A = torch.cat([gen_a_rows(torch, w, r, M // 8) for r in range(8)])
+    C = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    d = lib.gemm_desc(M, N, K, lib.BF16, lib.BF16)
+    s = torch.cuda.current_stream().cuda_stream
+    for _ in range(3):
+        lib.gemm_tn(d, A.data_ptr(), B.data_ptr(), C.data_ptr(), s)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(10):
+        lib.gemm_tn(d, A.data_ptr(), B.data_ptr(), C.data_ptr(), s)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / 10
+    chk = BandCheck(to_bits(torch, A), to_bits(torch, B), three_bands(M), K)
+    got, off = band_bits(torch, C, chk.bands)
+    tf = 2.0 * M * N * K / ms / 1e9
+    return {"workload": w["name"] + ", all rows on one GPU", "value": tf, "unit": UNIT, "ms_per_step": ms, "steps": 10,
+            "frac_of_sustained_peak": tf / pk.get("bf16_tflops_sustained", pk["bf16_tflops"]), "parity": chk.check(got, off),
+            "note": "N = 1 base of the strong-scaling curve; the N = 1 headline above is the 8192^3 configuration"}
 
 
 def bench_add(lib, torch, pk, n=1 << 28):
@@ -466,10 +713,13 @@ def bench_multi(lib, torch, copies=3):
     return out
 
 
-def bench_cublas(A, B, steps, warmup, flop, step, torch):
+def bench_cublas(A, B, steps, warmup, flop, step, torch, gpu_index=0):
     """torch.matmul (cuBLAS) on the same operands, the same number of back-to-back launches, the
     same GPU and process: a comparator beside the headline number, not part of it.  Long runs of
-    launches settle at the power cap, so the two are also timed in alternation (ten rounds of ten)."""
+    launches settle at the power cap, so the two are also timed in alternation (ten rounds of
+    thirty launches each), with the SM clock sampled during each side's rounds: time x clock is the
+    kernel's length in SM cycles, which separates what the power cap does to the clock from what
+    the kernel does with its cycles."""
     Bt = B.t()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
@@ -486,14 +736,23 @@ def bench_cublas(A, B, steps, warmup, flop, step, torch):
         mm()
     torch.cuda.synchronize()
     ms = timed(mm, steps)
-    ours, theirs = [], []
+    ours, theirs, mhz_ours, mhz_theirs = [], [], [], []
     for _ in range(10):
-        ours.append(timed(step, 10))
-        theirs.append(timed(mm, 10))
+        with ClockSampler(gpu_index) as c:
+            ours.append(timed(step, 30))
+        mhz_ours += c.samples
+        with ClockSampler(gpu_index) as c:
+            theirs.append(timed(mm, 30))
+        mhz_theirs += c.samples
     mo, mt = statistics.median(ours), statistics.median(theirs)
-    return {"value": flop / (ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms, "steps": steps,
-            "alternating": {"this_library_ms": mo, "cublas_ms": mt, "ratio": mo / mt,
-                            "how": "medians of ten rounds of ten launches each, the two in turn"}}
+    alt = {"this_library_ms": mo, "cublas_ms": mt, "ratio": mo / mt,
+           "how": "medians of ten rounds of thirty launches each, the two in turn"}
+    if mhz_ours and mhz_theirs:
+        fo, ft = statistics.median(mhz_ours), statistics.median(mhz_theirs)
+        alt.update({"this_library_sm_mhz": fo, "cublas_sm_mhz": ft, "this_library_kcycles": mo * fo, "cublas_kcycles": mt * ft,
+                    "cycles_ratio": (mo * fo) / (mt * ft),
+                    "cycles_how": "ms x median sampled SM MHz = thousands of SM cycles per launch (NVML clock samples of each side's rounds)"})
+    return {"value": flop / (ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms, "steps": steps, "alternating": alt}
 
 
 def bench_ref_kernel(A, B, M, N, K, torch):

@@ -30,7 +30,11 @@ EXPORTS = (
     "cute_b200_download", "cute_b200_free", "cute_b200_synchronize", "cute_b200_shard_rows",
     "cute_b200_gemm_tn_shard", "cute_b200_device_status", "cute_b200_launch_count", "cute_b200_alloc",
     "cute_b200_ipc_export", "cute_b200_ipc_open", "cute_b200_ipc_close", "cute_b200_copy_async", "cute_b200_gemm_tn_multi",
+    "cute_b200_gemm_layout_info", "cute_b200_comm_create", "cute_b200_comm_destroy", "cute_b200_comm_info",
+    "cute_b200_gemm_tn_sharded", "cute_b200_gemm_tn_sharded_host", "cute_b200_gemm_tn_multi_signal", "cute_b200_wait_signal",
 )
+
+REPLICATE_NONE, REPLICATE_AUTO, REPLICATE_FUSED, REPLICATE_COLLECTIVE, REPLICATE_COPIES = range(5)
 
 
 class GemmDesc(ctypes.Structure):
@@ -38,6 +42,16 @@ class GemmDesc(ctypes.Structure):
                 ("c_dtype", ctypes.c_int32), ("alpha", ctypes.c_float), ("beta", ctypes.c_float),
                 ("tile_n", ctypes.c_int32), ("cta_group", ctypes.c_int32), ("tile_m", ctypes.c_int32),
                 ("split_k", ctypes.c_int32), ("tuning", ctypes.c_int32 * 2)]
+
+
+class GemmLayout(ctypes.Structure):
+    """cute_b200_gemm_layout: the constants one GEMM tiling is compiled from."""
+    _fields_ = [(name, ctypes.c_uint32) for name in (
+        "instruction_descriptor", "umma_m", "umma_n", "umma_k", "block_k", "cta_rows", "a_stage_bytes", "b_stage_bytes",
+        "stage_bytes", "stages", "accumulator_halves", "half_columns", "accumulator_buffers", "tmem_columns", "threads",
+        "epilogue_warps", "full_arrivals", "empty_arrivals", "tmem_full_arrivals", "tmem_empty_arrivals",
+        "full_expect_tx_bytes", "push_chunk_bytes", "push_chunk_rows", "push_chunks_per_tile", "shared_memory_bytes",
+        "descriptor_k_step")] + [("smem_descriptor", ctypes.c_uint64)]
 
 
 class Arg(ctypes.Structure):
@@ -94,9 +108,18 @@ def load() -> ctypes.CDLL:
     L.cute_b200_ipc_close.argtypes = [u64]
     L.cute_b200_copy_async.argtypes = [u64, u64, u64, vp]
     L.cute_b200_gemm_tn_multi.argtypes = [ctypes.POINTER(GemmDesc), u64, u64, ctypes.POINTER(u64), i32, vp]
+    L.cute_b200_gemm_tn_multi_signal.argtypes = [ctypes.POINTER(GemmDesc), u64, u64, ctypes.POINTER(u64), ctypes.POINTER(u64), i32, vp]
+    L.cute_b200_wait_signal.argtypes = [u64, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32, vp]
     L.cute_b200_shard_rows.argtypes = [i32, i32, i32, ctypes.POINTER(i32), ctypes.POINTER(i32)]
     L.cute_b200_gemm_tn_shard.argtypes = [ctypes.POINTER(GemmDesc), i32, i32, u64, u64, u64, i32, vp]
     L.cute_b200_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint32 * 4)]
+    L.cute_b200_gemm_layout_info.argtypes = [i32, i32, i32, i32, i32, ctypes.c_uint32, ctypes.POINTER(GemmLayout)]
+    L.cute_b200_comm_create.argtypes = [i32, ctypes.POINTER(i32), ctypes.POINTER(vp)]
+    L.cute_b200_comm_destroy.argtypes = [vp]
+    L.cute_b200_comm_info.argtypes = [vp, ctypes.POINTER(i32 * 4)]
+    L.cute_b200_gemm_tn_sharded.argtypes = [vp, ctypes.POINTER(GemmDesc), ctypes.POINTER(u64), ctypes.POINTER(u64),
+                                            ctypes.POINTER(u64), i32]
+    L.cute_b200_gemm_tn_sharded_host.argtypes = [vp, ctypes.POINTER(GemmDesc), vp, vp, vp, ctypes.POINTER(ctypes.c_double)]
     L.cute_b200_launch_count.argtypes = []
     L.cute_b200_launch_count.restype = u64
     for name in EXPORTS:
@@ -137,6 +160,19 @@ def gemm_tn_multi(desc: GemmDesc, dA: int, dB: int, dC_list, stream: int = 0) ->
     """GEMM whose epilogue writes the result to every address in dC_list (own C and peers')."""
     arr = (ctypes.c_uint64 * len(dC_list))(*dC_list)
     check(load().cute_b200_gemm_tn_multi(ctypes.byref(desc), dA, dB, arr, len(dC_list), stream))
+
+
+def gemm_tn_multi_signal(desc: GemmDesc, dA: int, dB: int, dC_list, dSignal_list, stream: int = 0) -> None:
+    """gemm_tn_multi that adds 1 to the counter of every further destination's owner once the launch is complete."""
+    n = len(dC_list)
+    assert len(dSignal_list) == n
+    check(load().cute_b200_gemm_tn_multi_signal(ctypes.byref(desc), dA, dB, (ctypes.c_uint64 * n)(*dC_list),
+                                                (ctypes.c_uint64 * n)(*dSignal_list), n, stream))
+
+
+def wait_signal(dSignals: int, mask: int, at_least: int, timeout_ms: int = 30000, stream: int = 0) -> None:
+    """Queue the bounded wait for the counters dSignals[i], i in `mask`, on `stream`."""
+    check(load().cute_b200_wait_signal(dSignals, mask, at_least & 0xFFFFFFFF, timeout_ms, stream))
 
 
 def gemm_tn_static(desc: GemmDesc, dA: int, dB: int, dC: int, stream: int = 0) -> None:
@@ -240,6 +276,52 @@ def device_status() -> tuple[int, int, int, int]:
     out = (ctypes.c_uint32 * 4)()
     check(load().cute_b200_device_status(ctypes.byref(out)))
     return tuple(out)
+
+
+def comm_create(ordinals) -> int:
+    """One communicator over the listed devices of this process (an int n means devices 0 .. n-1)."""
+    if isinstance(ordinals, int):
+        ordinals = list(range(ordinals))
+    arr = (ctypes.c_int32 * len(ordinals))(*ordinals)
+    out = ctypes.c_void_p()
+    check(load().cute_b200_comm_create(len(ordinals), arr, ctypes.byref(out)))
+    return out.value
+
+
+def comm_destroy(comm: int) -> None:
+    check(load().cute_b200_comm_destroy(comm))
+
+
+def comm_info(comm: int) -> dict:
+    out = (ctypes.c_int32 * 4)()
+    check(load().cute_b200_comm_info(comm, ctypes.byref(out)))
+    return {"ngpus": out[0], "distinct": bool(out[1]), "peer_access": bool(out[2]), "collective_library": bool(out[3])}
+
+
+def gemm_tn_sharded(comm: int, desc: GemmDesc, dA_shards, dB, dC, replicate_c: int = REPLICATE_NONE) -> None:
+    """The row-sharded GEMM on every GPU of `comm`: one device pointer per GPU in each list; returns when all are done."""
+    n = len(dA_shards)
+    mk = lambda xs: (ctypes.c_uint64 * n)(*xs)
+    check(load().cute_b200_gemm_tn_sharded(comm, ctypes.byref(desc), mk(dA_shards), mk(dB), mk(dC), replicate_c))
+
+
+def gemm_tn_sharded_host(comm: int, desc: GemmDesc, hA: int, hB: int, hC: int) -> float:
+    """The same on whole host matrices (addresses); returns the duration of the call in seconds."""
+    sec = ctypes.c_double(0.0)
+    check(load().cute_b200_gemm_tn_sharded_host(comm, ctypes.byref(desc), hA, hB, hC, ctypes.byref(sec)))
+    return sec.value
+
+
+def gemm_layout_info(cta_group: int, tile_n: int, tile_m: int, ab_dtype: int = BF16, c_dtype: int = BF16,
+                     smem_addr: int = 0) -> GemmLayout:
+    """The constants the compiled kernel of this tiling uses (host arithmetic, no GPU needed)."""
+    out = GemmLayout()
+    check(load().cute_b200_gemm_layout_info(cta_group, tile_n, tile_m, ab_dtype, c_dtype, smem_addr, ctypes.byref(out)))
+    return out
+
+
+# Every (cta_group, tile_n, tile_m) the library instantiates.
+GEMM_TILINGS = [(g, n, m) for g in (1, 2) for n in (128, 256) for m in (128, 256)] + [(2, 128, 64), (2, 256, 64)]
 
 
 def launch_count() -> int:

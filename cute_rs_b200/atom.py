@@ -225,7 +225,10 @@ class Sm100UmmaOp:
     """tcgen05.mma.cta_group::{1,2}.kind::f16: one thread issues an
     (m x n x 16) MMA whose A and B come from shared memory through matrix
     descriptors and whose f32 accumulator lives in TMEM.  m counts the rows of
-    the whole CTA group (128 per CTA)."""
+    the whole CTA group: 128 per CTA, or 64 per CTA of a pair (m = 128,
+    cta_group = 2), whose accumulator still fills all 128 TMEM lanes of each
+    CTA: lanes 0-63 hold its 64 rows for columns [0, n/2), lanes 64-127 the
+    same rows for columns [n/2, n)."""
     ab_dtype: DType
     m: int
     n: int
@@ -234,8 +237,8 @@ class Sm100UmmaOp:
     def __post_init__(self):
         if self.ab_dtype not in (DType.F16, DType.BF16):
             raise ValueError("Sm100UmmaOp takes f16 or bf16 operands")
-        if self.cta_group not in (1, 2) or self.m != 128 * self.cta_group:
-            raise ValueError("Sm100UmmaOp: m must be 128 per CTA of the group")
+        if self.cta_group not in (1, 2) or self.m not in ((128,) if self.cta_group == 1 else (128, 256)):
+            raise ValueError("Sm100UmmaOp: m must be 128 per CTA of the group, or 64 per CTA of a pair")
         if self.n % 16 or not 16 <= self.n <= 256:
             raise ValueError("Sm100UmmaOp: n must be a multiple of 16 in [16, 256]")
 
@@ -248,8 +251,20 @@ class Sm100UmmaOp:
         fmt = 1 if self.ab_dtype == DType.BF16 else 0
         return (1 << 4) | (fmt << 7) | (fmt << 10) | ((self.n >> 3) << 17) | ((self.m >> 4) << 24)
 
+    @property
+    def rows_per_cta(self) -> int:
+        return self.m // self.cta_group
+
+    @property
+    def tmem_columns(self) -> int:
+        """TMEM columns one accumulator takes in each CTA."""
+        return self.n // 2 if self.rows_per_cta == 64 else self.n
+
     def tmem_coord(self, m: int, n: int, column0: int = 0):
         """(CTA of the group, TMEM lane, TMEM column) holding accumulator element (m, n)."""
+        if self.rows_per_cta == 64:
+            half = self.n // 2
+            return m // 64, m % 64 + 64 * (n // half), column0 + n % half
         return m // 128, m % 128, column0 + n
 
 

@@ -13,7 +13,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libcute_b200.so")
-SOURCES = ["api.cu", "elementwise_sm100.cu", "sgemm_sm100.cu", "gemm_sm100.cu"]
+SOURCES = ["api.cu", "elementwise_sm100.cu", "sgemm_sm100.cu", "gemm_sm100.cu", "multi_gpu.cu"]
 HEADERS = ["common.cuh", "ptx_sm100.cuh", os.path.join("..", "..", "include", "cute_b200.h")]
 
 
@@ -55,7 +55,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if failed:
         raise RuntimeError("nvcc failed")
     tmp = LIB + ".tmp"
-    subprocess.run([nvcc_path(), "-shared", "-o", tmp, *objs, "-cudart", "static"], check=True)
+    subprocess.run([nvcc_path(), "-shared", "-o", tmp, *objs, "-cudart", "static", "-ldl", "-lpthread"], check=True)
     os.replace(tmp, LIB)
     return LIB
 

@@ -280,11 +280,17 @@ def run(programs: dict, barriers: dict, seed: int = 0, tma_bytes_to=None, max_bu
 
 # ---- the GEMM kernel's protocol ------------------------------------------------------
 def gemm_schedule(cta_group: int = 2, stages: int = 4, mh: int = 2, acc_bufs: int = 1, units=(8, 8, 8),
-                  stage_bytes: int = 48 * 1024, mutations=(), push_chunks: int = 0):
+                  stage_bytes: int = 48 * 1024, mutations=(), push_chunks: int = 0, epilogue_warps: int = 8,
+                  tmem_empty_arrivals: int = None, expect_tx: int = None, push_bytes: int = 16 * 1024):
     """Programs and barriers of gemm_tn_kernel for one cluster.
 
     `units` lists the k-block count of each work unit the cluster processes (0 =
-    an empty k range).  Mutations (protocol bugs for the tests):
+    an empty k range).  `tmem_empty_arrivals` (count the accumulator-free barriers
+    are initialised with) and `expect_tx` (bytes the leader announces per stage)
+    default to what the schedule itself implies - one arrival per epilogue warp of
+    the group, every CTA's stage bytes; `tiling_from_library` passes the values the
+    compiled kernel uses instead, so that a kernel whose constants disagree with its
+    own schedule fails here.  Mutations (protocol bugs for the tests):
       "producer_skips_empty_wait"  the producer refills a stage without waiting for its release
       "mma_skips_full_wait"        the MMA issuer does not wait for the loads
       "mma_skips_tmem_wait"        ... nor for the epilogue to drain the accumulator
@@ -312,14 +318,14 @@ def gemm_schedule(cta_group: int = 2, stages: int = 4, mh: int = 2, acc_bufs: in
         for c in ctas:
             barriers[f"tfull{c}.{b}"] = 1
         for h in range(mh):
-            barriers[f"tempty.{b}.{h}"] = 8 * cta_group  # one arrival per epilogue warp of the group
+            # one arrival per epilogue warp of the group, unless the caller says what the kernel uses
+            barriers[f"tempty.{b}.{h}"] = tmem_empty_arrivals if tmem_empty_arrivals is not None else epilogue_warps * cta_group
     programs = {f"producer{c}": [] for c in ctas}
     programs["mma"] = []
     for c in ctas:
-        for w in range(8):
+        for w in range(epilogue_warps):
             programs[f"epilogue{c}.{w}"] = []
 
-    push_bytes = 16 * 1024
     if push_chunks:
         for c in ctas:
             barriers[f"push{c}.0"] = 1
@@ -337,7 +343,7 @@ def gemm_schedule(cta_group: int = 2, stages: int = 4, mh: int = 2, acc_bufs: in
                 if "producer_skips_empty_wait" not in mut:
                     p.append(("wait", f"empty{c}.{s}", rnd - 1 + (1 if "wrong_empty_parity" in mut else 0)))
                 if c == 0:
-                    total = stage_bytes * (1 if "expect_tx_short" in mut else cta_group)
+                    total = stage_bytes if "expect_tx_short" in mut else (expect_tx if expect_tx is not None else stage_bytes * cta_group)
                     p.append(("expect", f"full.{s}", total))
                 p.append(("tma", c, s, stage_bytes, f"full.{s}"))
             mma = programs["mma"]
@@ -355,7 +361,7 @@ def gemm_schedule(cta_group: int = 2, stages: int = 4, mh: int = 2, acc_bufs: in
             for c in ctas:
                 programs["mma"].append(("commit", f"tfull{c}.{buf}"))
             for c in ctas:
-                for w in range(8):
+                for w in range(epilogue_warps):
                     e = programs[f"epilogue{c}.{w}"]
                     e.append(("wait", f"tfull{c}.{buf}", use))
                     for h in range(mh):
@@ -376,14 +382,14 @@ def gemm_schedule(cta_group: int = 2, stages: int = 4, mh: int = 2, acc_bufs: in
                 # the chunk before have read the buffer it fills (the kernel's loop, unrolled).
                 for c in ctas:
                     p = programs[f"pusher{c}"]
-                    parts = [f"c{c}.{it}.{w}" for w in range(8)]
+                    parts = [f"c{c}.{it}.{w}" for w in range(epilogue_warps)]
                     for ch in range(push_chunks):
                         g = pushed + ch
                         if ch == 0 and "pusher_skips_tile_wait" not in mut:
                             if "shared_tile_counter" in mut:
-                                p.append(("wait_count", f"stored{c}", 8 * (it + 1)))
+                                p.append(("wait_count", f"stored{c}", epilogue_warps * (it + 1)))
                             else:
-                                p.extend(("wait_count", f"stored{c}.{w}", it + 1) for w in range(8))
+                                p.extend(("wait_count", f"stored{c}.{w}", it + 1) for w in range(epilogue_warps))
                         if g > 0 and "pusher_skips_read_wait" not in mut:
                             p.append(("wait_read", 1))
                         p.append(("expect", f"push{c}.{g % 2}", push_bytes))
@@ -396,6 +402,18 @@ def gemm_schedule(cta_group: int = 2, stages: int = 4, mh: int = 2, acc_bufs: in
                 pushed += push_chunks
             it += 1
     return programs, barriers
+
+
+def tiling_from_library(info, cta_group: int) -> dict:
+    """gemm_schedule's arguments for a tiling as the compiled kernel has it: `info`
+    is the cute_b200_gemm_layout the library reports (ring depth, stage bytes,
+    accumulator halves and buffers, epilogue warps, barrier counts, pusher chunk)."""
+    assert (info.full_arrivals, info.empty_arrivals, info.tmem_full_arrivals) == (1, 1, 1), \
+        "the schedule models one producer arrival, one commit per stage and one per accumulator"
+    return dict(cta_group=cta_group, stages=info.stages, mh=info.accumulator_halves, acc_bufs=info.accumulator_buffers,
+                stage_bytes=info.stage_bytes, epilogue_warps=info.epilogue_warps,
+                tmem_empty_arrivals=info.tmem_empty_arrivals, expect_tx=info.full_expect_tx_bytes,
+                push_bytes=info.push_chunk_bytes)
 
 
 def check_gemm(seeds=range(4), **kw) -> None:

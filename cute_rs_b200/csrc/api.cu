@@ -121,7 +121,7 @@ static cute_b200_status read_status(uint32_t out[4]) {
     return CUTE_B200_OK;
 }
 
-static cute_b200_status sync_and_check() {
+cute_b200_status sync_and_check() {
     uint32_t st[4];
     CB_TRY(read_status(st));
     if (st[0] != 0)
@@ -567,7 +567,22 @@ cute_b200_status cute_b200_gemm_tn_multi(const cute_b200_gemm_desc *desc, uint64
     if (!desc) return fail(CUTE_B200_ERR_NULL_POINTER, "gemm_tn_multi: desc is null");
     DeviceState *dev;
     CB_TRY(current_device(&dev));
-    return gemm_tn_multi(*desc, dA, dB, dC_list, count, static_cast<cudaStream_t>(stream), *dev);
+    return gemm_tn_multi(*desc, dA, dB, dC_list, count, nullptr, static_cast<cudaStream_t>(stream), *dev);
+}
+
+cute_b200_status cute_b200_gemm_tn_multi_signal(const cute_b200_gemm_desc *desc, uint64_t dA, uint64_t dB, const uint64_t *dC_list,
+                                                const uint64_t *dSignal_list, int32_t count, void *stream) {
+    if (!desc) return fail(CUTE_B200_ERR_NULL_POINTER, "gemm_tn_multi_signal: desc is null");
+    if (!dSignal_list) return fail(CUTE_B200_ERR_NULL_POINTER, "gemm_tn_multi_signal: the list of counters is null");
+    DeviceState *dev;
+    CB_TRY(current_device(&dev));
+    return gemm_tn_multi(*desc, dA, dB, dC_list, count, dSignal_list, static_cast<cudaStream_t>(stream), *dev);
+}
+
+cute_b200_status cute_b200_wait_signal(uint64_t dSignals, uint32_t mask, uint32_t at_least, uint32_t timeout_ms, void *stream) {
+    DeviceState *dev;
+    CB_TRY(current_device(&dev));
+    return wait_signal(dSignals, mask, at_least, timeout_ms, static_cast<cudaStream_t>(stream), *dev);
 }
 
 cute_b200_status cute_b200_gemm_tn_static(const cute_b200_gemm_desc *desc, uint64_t dA, uint64_t dB, uint64_t dC,
@@ -781,9 +796,32 @@ cute_b200_status cute_b200_gemm_tn_shard(const cute_b200_gemm_desc *desc, int32_
     return cute_b200_gemm_tn(&d, dA_shard, dB, dC, stream);
 }
 
+cute_b200_status cute_b200_comm_create(int32_t ngpus, const int32_t *ordinals, void **comm_out) {
+    return comm_create(ngpus, ordinals, comm_out);
+}
+
+cute_b200_status cute_b200_comm_destroy(void *comm) { return comm_destroy(comm); }
+
+cute_b200_status cute_b200_comm_info(void *comm, int32_t out[4]) { return comm_info(comm, out); }
+
+cute_b200_status cute_b200_gemm_tn_sharded(void *comm, const cute_b200_gemm_desc *desc, const uint64_t *dA_shard,
+                                           const uint64_t *dB, const uint64_t *dC, int32_t replicate_c) {
+    return gemm_tn_sharded(comm, desc, dA_shard, dB, dC, replicate_c);
+}
+
+cute_b200_status cute_b200_gemm_tn_sharded_host(void *comm, const cute_b200_gemm_desc *desc, const void *hA, const void *hB,
+                                                void *hC, double *seconds) {
+    return gemm_tn_sharded_host(comm, desc, hA, hB, hC, seconds);
+}
+
 cute_b200_status cute_b200_device_status(uint32_t out[4]) {
     if (!out) return fail(CUTE_B200_ERR_NULL_POINTER, "device_status: null output");
     return read_status(out);
+}
+
+cute_b200_status cute_b200_gemm_layout_info(int32_t cta_group, int32_t tile_n, int32_t tile_m, int32_t ab_dtype,
+                                            int32_t c_dtype, uint32_t smem_addr, cute_b200_gemm_layout *out) {
+    return gemm_layout_info(cta_group, tile_n, tile_m, ab_dtype, c_dtype, smem_addr, out);
 }
 
 uint64_t cute_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }

@@ -50,12 +50,17 @@ cute_b200_status sgemm_nt(int m, int n, int k, float alpha, float beta, const fl
                           cudaStream_t stream, const DeviceState &dev);
 cute_b200_status gemm_tn(const cute_b200_gemm_desc &desc, uint64_t a, uint64_t b, uint64_t c, cudaStream_t stream,
                          const DeviceState &dev);
+// signal_list: null, or `count` addresses of which [1..] are counters that receive +1 when the launch is complete.
 cute_b200_status gemm_tn_multi(const cute_b200_gemm_desc &desc, uint64_t a, uint64_t b, const uint64_t *c_list, int count,
-                               cudaStream_t stream, const DeviceState &dev);
+                               const uint64_t *signal_list, cudaStream_t stream, const DeviceState &dev);
+cute_b200_status wait_signal(uint64_t counter, uint32_t mask, uint32_t at_least, uint32_t timeout_ms, cudaStream_t stream,
+                             const DeviceState &dev);
 // The same GEMM writing an m x n block of a wider row-major C: ldc elements between rows (>= n).
 // Never splits k (the second pass of a split assumes a dense C); k must be positive.
 cute_b200_status gemm_tn_strided(const cute_b200_gemm_desc &desc, uint64_t a, uint64_t b, uint64_t c, int ldc,
                                  cudaStream_t stream, const DeviceState &dev);
+cute_b200_status gemm_layout_info(int cta_group, int tile_n, int tile_m, int ab_dtype, int c_dtype, uint32_t smem_addr,
+                                  cute_b200_gemm_layout *out);
 cute_b200_status gemm_tn_init(const DeviceState &dev);
 void gemm_tn_release_scratch();
 cute_b200_status gemm_tn_static(const cute_b200_gemm_desc &desc, uint64_t a, uint64_t b, uint64_t c, cudaStream_t stream,
@@ -63,5 +68,15 @@ cute_b200_status gemm_tn_static(const cute_b200_gemm_desc &desc, uint64_t a, uin
 // Device address of the status words gemm_tn_static owns on `device`, null until that entry point has run there.
 uint32_t *gemm_tn_static_status_words(int device);
 cute_b200_status sgemm_nt_init(const DeviceState &dev);
+// Waits for the current device and turns a kernel's bounded-wait report into CUTE_B200_ERR_DEVICE_TIMEOUT.
+cute_b200_status sync_and_check();
+// The launcher for several GPUs (multi_gpu.cu).
+cute_b200_status comm_create(int ngpus, const int *ordinals, void **comm_out);
+cute_b200_status comm_destroy(void *comm);
+cute_b200_status comm_info(void *comm, int32_t out[4]);
+cute_b200_status gemm_tn_sharded(void *comm, const cute_b200_gemm_desc *desc, const uint64_t *dA_shard, const uint64_t *dB,
+                                 const uint64_t *dC, int replicate_c);
+cute_b200_status gemm_tn_sharded_host(void *comm, const cute_b200_gemm_desc *desc, const void *hA, const void *hB, void *hC,
+                                      double *seconds);
 
 }  // namespace cb

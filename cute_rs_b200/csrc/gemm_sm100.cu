@@ -57,7 +57,11 @@ constexpr int UMMA_K = 16;     // k per tcgen05.mma for 16-bit inputs
 constexpr uint32_t RING_BYTES = 192 * 1024;
 constexpr uint32_t PUSH_BUF_BYTES = 16 * 1024;  // one chunk of a finished tile on its way to the other GPUs
 constexpr uint32_t STAGING_BYTES = 2 * PUSH_BUF_BYTES;
-constexpr uint32_t BAR_BYTES = 256;
+constexpr uint32_t BAR_BYTES = 512;
+constexpr int MAX_STAGES = 12;
+constexpr uint32_t DESC_K_STEP = (UMMA_K * 2) >> 4;  // one MMA's k (16 elements = 32 bytes) in units of the descriptor's address field
+// Rows of one pusher chunk: whole tile rows of bn columns filling one staging buffer.
+__host__ __device__ constexpr int push_rows(int bn, bool c_bf16) { return int(PUSH_BUF_BYTES) / (bn * (c_bf16 ? 2 : 4)); }
 constexpr uint64_t WAIT_LIMIT_NS = 4ull * 1000 * 1000 * 1000;
 
 // Report codes written to the status word.
@@ -67,7 +71,8 @@ enum : uint32_t {
     WHERE_MMA_TMEM = 3,
     WHERE_EPILOGUE = 4,
     WHERE_DRAIN = 5,
-    WHERE_PUSHER = 6
+    WHERE_PUSHER = 6,
+    WHERE_SIGNAL = 7  // cute_b200_wait_signal: the counter did not reach the expected value in time
 };
 
 #ifndef EPI_GROUPS_BIG
@@ -83,21 +88,46 @@ __host__ __device__ constexpr int num_threads(int bn, int mh) { return 64 + 128 
 // a CTA owns 256 rows of C, reuses every B block for two MMAs and so moves a
 // quarter less operand data per flop, at the price of a single-buffered
 // accumulator when BN == 256 (2 x 256 columns fill the 512 columns of TMEM).
+// MH == 0 is the 64-rows-per-CTA tile of a pair: one cta_group::2 MMA of
+// M = 128 whose accumulator keeps all 128 TMEM lanes busy with 64 rows - lanes
+// 0-63 hold columns [0, BN/2) of the CTA's rows, lanes 64-127 columns
+// [BN/2, BN) - in BN/2 TMEM columns.  Its stages are small (16 KiB at BN = 128),
+// so the ring is deep: the tile for problems with few row tiles and a long k,
+// which are bound by how fast A streams in from HBM.
 template <int CTA_GROUP, int BN, int MH>
 struct Cfg {
-    static constexpr int A_ROWS = BM * MH;         // A rows this CTA loads per stage
-    static constexpr int B_ROWS = BN / CTA_GROUP;  // B rows this CTA loads per stage
+    static constexpr bool HALF = MH == 0;
+    static_assert(!HALF || CTA_GROUP == 2, "the 64-row tile is a pair tile");
+    static constexpr int HALVES = HALF ? 1 : MH;                  // 128-lane accumulators per CTA
+    static constexpr int A_ROWS = HALF ? 64 : BM * MH;           // A rows this CTA loads per stage
+    static constexpr int B_ROWS = BN / CTA_GROUP;                 // B rows this CTA loads per stage
+    static constexpr int UMMA_M = (HALF ? 64 : BM) * CTA_GROUP;   // rows of one MMA over the whole group
     static constexpr uint32_t A_BYTES = A_ROWS * BK * 2;
     static constexpr uint32_t B_BYTES = B_ROWS * BK * 2;
     static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int STAGES = RING_BYTES / STAGE_BYTES;
-    static constexpr int ACC_COLS = MH * BN;                        // TMEM columns of one accumulator set
+    static constexpr int STAGES = (RING_BYTES / STAGE_BYTES) > MAX_STAGES ? MAX_STAGES : int(RING_BYTES / STAGE_BYTES);
+    static constexpr int HALF_COLS = HALF ? BN / 2 : BN;             // TMEM columns of one 128-lane accumulator
+    static constexpr int ACC_COLS = HALVES * HALF_COLS;              // TMEM columns of one accumulator set
     static constexpr int ACC_BUFS = (2 * ACC_COLS <= 512) ? 2 : 1;  // double buffered when it fits
-    static constexpr uint32_t TMEM_COLS = (ACC_COLS * ACC_BUFS <= 256) ? 256 : 512;
+    static constexpr uint32_t TMEM_COLS = (ACC_COLS * ACC_BUFS <= 128) ? 128 : ((ACC_COLS * ACC_BUFS <= 256) ? 256 : 512);
     static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + STAGING_BYTES + 1024 + BAR_BYTES;
-    static_assert(STAGES >= 2 && STAGES <= 12, "ring depth");
+    // Arrival counts of the mbarriers: the producer's arrive.expect_tx fills a stage, one tcgen05.commit
+    // frees it and one publishes an accumulator, every epilogue warp of the group hands a half back.
+    static constexpr uint32_t FULL_ARRIVALS = 1, EMPTY_ARRIVALS = 1, TFULL_ARRIVALS = 1;
+    static constexpr uint32_t TEMPTY_ARRIVALS = 4 * epilogue_groups(BN, MH) * CTA_GROUP;
+    static constexpr uint32_t EXPECT_TX = CTA_GROUP * STAGE_BYTES;  // bytes the (leader's) full barrier counts per stage
+    static_assert(STAGES >= 2 && STAGES <= MAX_STAGES, "ring depth");
     static_assert(ACC_COLS * ACC_BUFS <= 512, "accumulators exceed TMEM");
+    static_assert(SMEM_BYTES <= 227 * 1024, "shared memory");
 };
+
+// Instruction descriptor of tcgen05.mma.kind::f16: f32 accumulator (bit 4), A and B format (0 = f16,
+// 1 = bf16) at bits 7 and 10, both operands K-major (bits 15, 16 clear), N >> 3 at bit 17, M >> 4 at
+// bit 24, M counting the rows of the whole CTA group.
+__host__ __device__ constexpr uint32_t make_idesc(bool bf16, int umma_m, int bn) {
+    return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | (uint32_t(bn >> 3) << 17) |
+           (uint32_t(umma_m >> 4) << 24);
+}
 
 struct GemmParams {
     void *C;
@@ -118,6 +148,13 @@ struct GemmParams {
     int extra_count;
     void *extra_c[7];
     int push;
+    // Completion signal of the several-destination form: when every CTA of the launch has finished
+    // (all stores and pushes to every destination complete), the last one adds 1 to each of these
+    // counters, which live in the memory of the GPUs that own the destinations (release, system scope).
+    // `done_counter` is this GPU's count of finished CTAs; the last CTA sets it back to zero.
+    int signal_count;
+    uint32_t *signal[7];
+    uint32_t *done_counter;
 };
 
 // Tensor maps of C ([0]) and of its further copies, for the pusher warp: boxes of BN columns by
@@ -130,7 +167,7 @@ struct CMaps {
 // with the 128B swizzle (what TMA writes with CU_TENSOR_MAP_SWIZZLE_128B):
 // start address >> 4, leading byte offset 1 (unused by swizzled K-major),
 // stride byte offset 1024 (eight rows), descriptor version 1, layout 2.
-__device__ __forceinline__ uint64_t sw128_desc(uint32_t saddr) {
+__host__ __device__ __forceinline__ constexpr uint64_t sw128_desc(uint32_t saddr) {
     return uint64_t((saddr & 0x3FFFFu) >> 4) | (uint64_t(1) << 16) | (uint64_t(1024 >> 4) << 32) |
            (uint64_t(1) << 46) | (uint64_t(2) << 61);
 }
@@ -293,6 +330,7 @@ __global__ void __launch_bounds__(num_threads(BN, MH), 1)
     // count: a warp may run a tile or two ahead of another, and a sum could not tell whose parts are in.
     volatile uint32_t *tiles_stored = reinterpret_cast<volatile uint32_t *>(tail + 8);
     static_assert(8u * (2 * C::STAGES + 9) + 8u + 4u * 4 * EG <= BAR_BYTES, "barrier area");
+    constexpr int HALVES = C::HALVES;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = CTA_GROUP == 1 ? 0u : ptx::cluster_ctarank();
@@ -305,13 +343,13 @@ __global__ void __launch_bounds__(num_threads(BN, MH), 1)
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; s++) {
-            ptx::mbar_init(full_bar(s), 1);
-            ptx::mbar_init(empty_bar(s), 1);
+            ptx::mbar_init(full_bar(s), C::FULL_ARRIVALS);
+            ptx::mbar_init(empty_bar(s), C::EMPTY_ARRIVALS);
         }
         for (int buf = 0; buf < 2; buf++) {
-            ptx::mbar_init(tfull_bar(buf), 1);
+            ptx::mbar_init(tfull_bar(buf), C::TFULL_ARRIVALS);
             for (int h = 0; h < 2; h++)
-                ptx::mbar_init(tempty_bar(buf, h), 4 * EG * CTA_GROUP);  // one arrival per epilogue warp of the pair
+                ptx::mbar_init(tempty_bar(buf, h), C::TEMPTY_ARRIVALS);  // one arrival per epilogue warp of the pair
         }
         ptx::mbar_init(drain_bar, 1);
         ptx::mbar_init(push_bar(0), 1);
@@ -357,13 +395,13 @@ __global__ void __launch_bounds__(num_threads(BN, MH), 1)
                     if (p.debug & 1) {
                         if (rank == 0) ptx::mbar_arrive(full_bar(s));
                     } else if constexpr (CTA_GROUP == 1) {
-                        ptx::mbar_arrive_expect_tx(full_bar(s), C::STAGE_BYTES);
+                        ptx::mbar_arrive_expect_tx(full_bar(s), C::EXPECT_TX);
                         ptx::tma_load_2d(a_dst, &tmA, full_bar(s), kb * BK, row_a);
                         ptx::tma_load_2d(b_dst, &tmB, full_bar(s), kb * BK, row_b);
                     } else {
                         // Both CTAs' bytes are counted on the leader's barrier,
                         // which is the one the MMA issuer waits on.
-                        if (rank == 0) ptx::mbar_arrive_expect_tx(full_bar(s), 2 * C::STAGE_BYTES);
+                        if (rank == 0) ptx::mbar_arrive_expect_tx(full_bar(s), C::EXPECT_TX);
                         const uint32_t leader_full = ptx::mapa(full_bar(s), 0);
                         ptx::tma_load_2d_pair(a_dst, &tmA, leader_full, kb * BK, row_a);
                         ptx::tma_load_2d_pair(b_dst, &tmB, leader_full, kb * BK, row_b);
@@ -411,7 +449,7 @@ __global__ void __launch_bounds__(num_threads(BN, MH), 1)
                     const uint32_t a_src = ring + uint32_t(s) * C::STAGE_BYTES;
                     const uint64_t b_desc = sw128_desc(a_src + C::A_BYTES);
 #pragma unroll
-                    for (int h = 0; h < MH; h++) {
+                    for (int h = 0; h < HALVES; h++) {
                         if (kb == u.kb0) {
                             // The epilogue must have drained this half of the buffer
                             // (a fresh barrier passes at once).
@@ -425,8 +463,7 @@ __global__ void __launch_bounds__(num_threads(BN, MH), 1)
                         const uint64_t a_desc = sw128_desc(a_src + uint32_t(h) * (BM * BK * 2));
 #pragma unroll
                         for (int j = 0; j < BK / UMMA_K; j++) {
-                            // 16 elements of k = 32 bytes = 2 units of the address field
-                            ptx::umma_f16<CTA_GROUP>(d_tmem + uint32_t(h * BN), a_desc + 2u * j, b_desc + 2u * j, p.idesc,
+                            ptx::umma_f16<CTA_GROUP>(d_tmem + uint32_t(h * C::HALF_COLS), a_desc + DESC_K_STEP * j, b_desc + DESC_K_STEP * j, p.idesc,
                                                      (kb > u.kb0 || j > 0) ? 1u : 0u);
                         }
                         issued = true;
@@ -456,11 +493,14 @@ __global__ void __launch_bounds__(num_threads(BN, MH), 1)
     } else if (warp < 2 + 4 * EG) {
         // ------------------------------------------------------------ epilogue
         // EG groups of four warps: warp w reads TMEM lane quarter w % 4 (the only one
-        // it may address) and, of every 128-row half, every EG-th 32-column chunk.
+        // it may address) and, of every 128-lane accumulator, every EG-th 32-column chunk.
+        // In the 64-row tile lanes 64-127 hold the same rows as lanes 0-63, for the upper
+        // half of the tile's columns.
         const uint32_t q = uint32_t(warp) & 3u;
         const int e = (warp - 2) >> 2;
-        constexpr int CH = BN / 32 / EG;  // chunks per half per warp
-        constexpr int ITEMS = MH * CH;
+        constexpr int CH = C::HALF_COLS / 32 / EG;  // chunks per accumulator per warp
+        constexpr int ITEMS = HALVES * CH;
+        static_assert(CH >= 1, "every epilogue warp needs a chunk");
         const bool plain = (p.alpha == 1.0f && p.beta == 0.0f);
         bool ok = true;
         int it = 0;
@@ -480,12 +520,13 @@ __global__ void __launch_bounds__(num_threads(BN, MH), 1)
                 }
                 ptx::tc_fence_after();
             }
-            const int row0 = (tc.tm * CTA_GROUP + int(rank)) * C::A_ROWS + int(q) * 32 + lane;
+            const int row0 = (tc.tm * CTA_GROUP + int(rank)) * C::A_ROWS + (C::HALF ? int(q & 1u) : int(q)) * 32 + lane;
+            const int col_base = tc.tn * BN + (C::HALF ? int(q >> 1) * C::HALF_COLS : 0);
             const uint32_t taddr0 = tmem_base + ((q * 32u) << 16) + uint32_t(buf * C::ACC_COLS);
-            auto col_of = [&](int i) { return ((i % CH) * EG + e) * 32; };
+            auto col_of = [&](int i) { return ((i % CH) * EG + e) * 32; };  // within the accumulator's columns
             auto load = [&](int i, uint32_t(&v)[32]) {
                 if (have_acc) {
-                    ptx::tmem_ld_32x32(taddr0 + uint32_t((i / CH) * BN + col_of(i)), v);
+                    ptx::tmem_ld_32x32(taddr0 + uint32_t((i / CH) * C::HALF_COLS + col_of(i)), v);
                 } else {
 #pragma unroll
                     for (int j = 0; j < 32; j++) v[j] = 0u;
@@ -503,10 +544,10 @@ __global__ void __launch_bounds__(num_threads(BN, MH), 1)
                     }
                 }
                 if (p.debug & 2) return;
-                store_chunk<C_BF16>(p, cbase, row0 + (i / CH) * BM, tc.tn * BN + col_of(i), v, plain);
+                store_chunk<C_BF16>(p, cbase, row0 + (i / CH) * BM, col_base + col_of(i), v, plain);
                 if (!p.push)
                     for (int d = 0; d < p.extra_count; d++)
-                        store_chunk<C_BF16>(p, p.extra_c[d], row0 + (i / CH) * BM, tc.tn * BN + col_of(i), v, true);
+                        store_chunk<C_BF16>(p, p.extra_c[d], row0 + (i / CH) * BM, col_base + col_of(i), v, true);
             };
             // Two register buffers: the TMEM read of the next chunk is in flight
             // while the current one is converted and stored.
@@ -541,7 +582,7 @@ __global__ void __launch_bounds__(num_threads(BN, MH), 1)
         // tensor store per destination.  It runs behind the epilogue and beside the main loop of
         // the following tiles; nothing but the end of the kernel waits for it.
         if (p.push && lane == 0) {
-            constexpr int PUSH_ROWS = int(PUSH_BUF_BYTES) / (BN * (C_BF16 ? 2 : 4));
+            constexpr int PUSH_ROWS = push_rows(BN, C_BF16);
             constexpr int CHUNKS = C::A_ROWS / PUSH_ROWS;
             static_assert(PUSH_ROWS >= 8 && C::A_ROWS % PUSH_ROWS == 0, "push chunk shape");
             for (int d = 0; d <= p.extra_count; d++) ptx::prefetch_tensormap(&tmC.m[d]);
@@ -607,6 +648,49 @@ __global__ void __launch_bounds__(num_threads(BN, MH), 1)
         ptx::cluster_wait();
     }
     if (warp == 1) ptx::tmem_dealloc<CTA_GROUP>(tmem_base, C::TMEM_COLS);
+    // Everything this CTA stored, to its own C and to the other destinations (the pusher's thread has
+    // waited for its bulk stores), is ordered before this point by the barrier above.  The last CTA
+    // of the launch tells the owners of the destinations.  Every CTA counts itself (low half of the
+    // word), one that gave up also in the high half; if any did, nothing is signalled, so that the
+    // owners' waits run out and report as well.
+    if (p.signal_count > 0 && threadIdx.x == 0) {
+        ptx::fence_proxy_async_global();
+        __threadfence();
+        const uint32_t mine = 1u + (*abort_flag ? 0x10000u : 0u);
+        const uint32_t all = atomicAdd(p.done_counter, mine) + mine;
+        if ((all & 0xffffu) == gridDim.x) {
+            *p.done_counter = 0u;  // the next launch on this device counts from zero again
+            if ((all >> 16) == 0u) {
+                __threadfence_system();
+                for (int i = 0; i < p.signal_count; i++) ptx::red_release_sys_add(p.signal[i], 1u);
+            }
+        }
+    }
+}
+
+// Waits until every counter[i] with bit i of `mask` set has reached at_least (acquire, system scope,
+// compared as wrapping 32-bit counts) or the limit runs out; then reports {WHERE_SIGNAL, at_least,
+// index of the counter that was short, its value} in the status word and returns.
+__global__ void wait_signal_kernel(const uint32_t *counter, uint32_t mask, uint32_t at_least, uint64_t limit_ns, uint32_t *status) {
+    if (threadIdx.x != 0) return;
+    const uint64_t t0 = ptx::globaltimer_ns();
+    for (int i = 0; i < 32; i++) {
+        if (!((mask >> i) & 1u)) continue;
+        uint32_t seen = ptx::ld_acquire_sys(counter + i);
+        while (int32_t(seen - at_least) < 0) {
+            if (ptx::globaltimer_ns() - t0 > limit_ns) {
+                if (atomicCAS(status, 0u, uint32_t(WHERE_SIGNAL)) == 0u) {
+                    status[1] = at_least;
+                    status[2] = uint32_t(i);
+                    status[3] = seen;
+                    __threadfence();
+                }
+                return;
+            }
+            __nanosleep(200);
+            seen = ptx::ld_acquire_sys(counter + i);
+        }
+    }
 }
 
 // out = alpha * 0 + beta * c (or 0 when C is write-only): the k == 0 case.
@@ -742,7 +826,7 @@ template <int CTA_GROUP, int BN, int MH, bool C_BF16>
 cute_b200_status launch(const CUtensorMap &tmA, const CUtensorMap &tmB, const CMaps &tmC, GemmParams p,
                         int sm_count, cudaStream_t stream) {
     using C = Cfg<CTA_GROUP, BN, MH>;
-    const int tile_rows = BM * MH * CTA_GROUP;
+    const int tile_rows = C::A_ROWS * CTA_GROUP;
     p.m_tiles = (p.M + tile_rows - 1) / tile_rows;
     p.n_tiles = (p.N + BN - 1) / BN;
     const long long tiles = (long long)p.m_tiles * p.n_tiles * p.splits;
@@ -785,11 +869,14 @@ cute_b200_status set_smem_limit() {
     X(1, 128, 1, false) X(1, 128, 1, true) X(1, 256, 1, false) X(1, 256, 1, true) \
     X(2, 128, 1, false) X(2, 128, 1, true) X(2, 256, 1, false) X(2, 256, 1, true) \
     X(1, 128, 2, false) X(1, 128, 2, true) X(1, 256, 2, false) X(1, 256, 2, true) \
-    X(2, 128, 2, false) X(2, 128, 2, true) X(2, 256, 2, false) X(2, 256, 2, true)
+    X(2, 128, 2, false) X(2, 128, 2, true) X(2, 256, 2, false) X(2, 256, 2, true) \
+    X(2, 128, 0, false) X(2, 128, 0, true) X(2, 256, 0, false) X(2, 256, 0, true)
 
 // Relative mainloop efficiency of a tiling, measured on 8192^3 bf16 (the 512 x 256
-// pair tile is the reference point); used only to rank candidates.
+// pair tile is the reference point); used only to rank candidates.  mh counts the
+// 128-row accumulators per CTA, 0 = the 64-row pair tile.
 double tiling_efficiency(int group, int bn, int mh) {
+    if (mh == 0) return bn == 128 ? 0.55 : 0.70;
     double e = 1.0;
     if (group == 1) e *= (mh == 2 ? 0.96 : 0.86);
     else if (mh == 1) e *= 0.92;
@@ -799,15 +886,18 @@ double tiling_efficiency(int group, int bn, int mh) {
 
 // Pick tiling and k split with the smallest estimated time.  A launch runs
 // whole waves of work units (tile x k range) over the clusters that fit; a
-// unit costs its MMA time plus a fixed start/drain latency; a split GEMM also
-// pays a second pass over the f32 partial planes.
+// unit costs its MMA time plus a fixed start/drain latency, or the time its
+// share of HBM bandwidth needs to bring its rows of A in, whichever is longer;
+// a split GEMM also pays a second pass over the f32 partial planes.
 //
-// want_* != 0 fixes that choice.  A caller's want_splits > 1 is honoured as it
-// is (cut down to the number of k blocks and to max_splits), whether or not
-// the cost model would have picked it; with want_splits == 0 the splits
-// min_splits..max_splits compete, and a split above min_splits must leave each
-// range at least four k blocks.  Returns the estimate in seconds.
-double choose_tiling(int m, int n, int k, int c_bytes, int sm_count, int want_group, int want_bn, int want_mh,
+// want_* != 0 fixes that choice (want_rows: rows of C per CTA, 64, 128 or 256).
+// A caller's want_splits > 1 is honoured as it is (cut down to the number of k
+// blocks and to max_splits), whether or not the cost model would have picked
+// it; with want_splits == 0 the splits min_splits..max_splits compete, and a
+// split above min_splits must leave each range at least four k blocks.
+// *mh receives the 128-row accumulators per CTA, 0 for the 64-row pair tile.
+// Returns the estimate in seconds.
+double choose_tiling(int m, int n, int k, int c_bytes, int sm_count, int want_group, int want_bn, int want_rows,
                      int want_splits, int min_splits, int max_splits, int *group, int *bn, int *mh, int *splits) {
     const double sm_rate = 1.0e13;       // dense 16-bit flop/s of one SM at the clocks a GEMM sustains
     const double unit_latency = 2.5e-6;  // fill the ring, drain the accumulator
@@ -826,21 +916,27 @@ double choose_tiling(int m, int n, int k, int c_bytes, int sm_count, int want_gr
     if (want_splits > 0) {
         s_lo = s_hi = want_splits < min_splits ? min_splits : (want_splits > max_splits ? max_splits : want_splits);
     }
+    if (want_rows == 64) want_group = 2;  // the 64-row tile exists as a pair tile only
     double best = 1e300;
     for (int g = 1; g <= 2; g++)
         for (int b = 128; b <= 256; b += 128)
-            for (int h = 1; h <= 2; h++)
+            for (int h = 0; h <= 2; h++)
                 for (int s = s_lo; s <= s_hi; s++) {
-                    if ((want_group && g != want_group) || (want_bn && b != want_bn) || (want_mh && h != want_mh)) continue;
+                    const int cta_rows = h == 0 ? 64 : 128 * h;
+                    if (h == 0 && g != 2) continue;
+                    if ((want_group && g != want_group) || (want_bn && b != want_bn) || (want_rows && cta_rows != want_rows)) continue;
                     if (want_splits == 0 && s > min_splits && (s > k_blocks / 4 || double(s) * m * n * 4 > 512e6)) continue;
-                    const long long rows = 128LL * g * h;
+                    const long long rows = (long long)cta_rows * g;
                     const long long units = ((m + rows - 1) / rows) * ((n + b - 1) / b) * s;
                     const long long clusters = sm_count / g;
                     const long long waves = (units + clusters - 1) / clusters;
                     const int kb_per = (k_blocks + s - 1) / s;
-                    const double unit_time =
-                        2.0 * rows * b * kb_per * BK / (g * sm_rate * tiling_efficiency(g, b, h)) + unit_latency;
-                    double t = waves * unit_time;
+                    double unit_time = 2.0 * rows * b * kb_per * BK / (g * sm_rate * tiling_efficiency(g, b, h));
+                    // the units of a wave share the HBM bandwidth for their rows of A (B stays in L2)
+                    const long long in_wave = units < clusters ? units : clusters;
+                    const double stream_time = double(in_wave) * rows * kb_per * BK * 2 / hbm;
+                    if (stream_time > unit_time) unit_time = stream_time;
+                    double t = waves * (unit_time + unit_latency);
                     if (g == 2) t += pair_start;
                     if (s > 1) t += (double(s + 1) * m * n * 4 + double(m) * n * c_bytes) / hbm + 3e-6;
                     if (t < best) {
@@ -955,7 +1051,7 @@ cute_b200_status gemm_tn_static(const cute_b200_gemm_desc &d, uint64_t a, uint64
         return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "gemm_tn_static: f16/bf16 inputs and f32/bf16 output only");
     if (d.k % 8) return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "gemm_tn_static: k must be a multiple of 8, got %d", d.k);
     if ((d.tile_n != 0 && d.tile_n != 128 && d.tile_n != 256) || d.cta_group < 0 || d.cta_group > 2 ||
-        (d.tile_m != 0 && d.tile_m != 128 && d.tile_m != 256))
+        (d.tile_m != 0 && d.tile_m != 64 && d.tile_m != 128 && d.tile_m != 256) || (d.tile_m == 64 && d.cta_group == 1))
         return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "gemm_tn_static: invalid tile_n, tile_m or cta_group");
     if (d.split_k == 1 || d.split_k < 0 || d.split_k > 16)
         return fail(CUTE_B200_ERR_INVALID_ARGUMENT,
@@ -983,7 +1079,7 @@ cute_b200_status gemm_tn_static(const cute_b200_gemm_desc &d, uint64_t a, uint64
     // The tiling comes from the same cost model as the allocating path, asked for at least
     // two ranges and at most what the built-in array (and k) allow.
     int group = 2, bn = 256, mh = 2, splits = 2;
-    choose_tiling(d.m, d.n, d.k, c_bf16 ? 2 : 4, setup->sm_count, d.cta_group, d.tile_n, d.tile_m / 128, d.split_k, 2,
+    choose_tiling(d.m, d.n, d.k, c_bf16 ? 2 : 4, setup->sm_count, d.cta_group, d.tile_n, d.tile_m, d.split_k, 2,
                   int(max_splits_by_scratch < 16 ? max_splits_by_scratch : 16), &group, &bn, &mh, &splits);
 
     GemmParams p = {};
@@ -1000,11 +1096,11 @@ cute_b200_status gemm_tn_static(const cute_b200_gemm_desc &d, uint64_t a, uint64
     p.splits = splits;
     p.split_stride = plane * 4;
     p.c_vec_ok = (size_t(d.n) * 4) % 32 == 0 ? 2 : ((size_t(d.n) * 4) % 16 == 0 ? 1 : 0);
-    const uint32_t fmt = d.ab_dtype == CUTE_B200_BF16 ? 1u : 0u;
-    p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(bn >> 3) << 17) | (uint32_t((BM * group) >> 4) << 24);
+    const int cta_rows = mh == 0 ? 64 : BM * mh;
+    p.idesc = make_idesc(d.ab_dtype == CUTE_B200_BF16, (mh == 0 ? 64 : BM) * group, bn);
 
     CUtensorMap tmA, tmB;
-    CB_TRY(make_tensor_map(&tmA, a, d.ab_dtype, d.m, d.k, BM * mh));
+    CB_TRY(make_tensor_map(&tmA, a, d.ab_dtype, d.m, d.k, cta_rows));
     CB_TRY(make_tensor_map(&tmB, b, d.ab_dtype, d.n, d.k, bn / group));
     cute_b200_status st = CUTE_B200_ERR_UNSUPPORTED;
 #define CB_CASE(G, N_, H, BF) \
@@ -1045,12 +1141,25 @@ struct GemmExtras {
     const uint64_t *extra_c = nullptr;
     int extra_count = 0;
     int ldc = 0;  // 0 = n
+    const uint64_t *signal = nullptr;  // extra_count counters to add 1 to when the launch is complete, or null
 };
 static cute_b200_status gemm_tn_ex(const cute_b200_gemm_desc &d, uint64_t a, uint64_t b, uint64_t c, cudaStream_t stream,
                                    const DeviceState &dev, const GemmExtras &ex);
 
+cute_b200_status wait_signal(uint64_t counter, uint32_t mask, uint32_t at_least, uint32_t timeout_ms, cudaStream_t stream,
+                             const DeviceState &dev) {
+    if (!counter || (counter & 3u)) return fail(CUTE_B200_ERR_MISALIGNED, "wait_signal: the counters are null or not 4-byte aligned");
+    if (timeout_ms == 0 || timeout_ms > 600000u)
+        return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "wait_signal: the limit must be 1 ms to 10 min, got %u ms", timeout_ms);
+    wait_signal_kernel<<<1, 32, 0, stream>>>(reinterpret_cast<const uint32_t *>(counter), mask, at_least,
+                                             uint64_t(timeout_ms) * 1000000ull, dev.status_word);
+    CB_CUDA(cudaGetLastError());
+    count_launch();
+    return CUTE_B200_OK;
+}
+
 cute_b200_status gemm_tn_multi(const cute_b200_gemm_desc &d, uint64_t a, uint64_t b, const uint64_t *c_list, int count,
-                               cudaStream_t stream, const DeviceState &dev) {
+                               const uint64_t *signal_list, cudaStream_t stream, const DeviceState &dev) {
     if (!c_list || count < 1 || count > 8)
         return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "gemm_tn_multi: 1 to 8 destinations, got %d", count);
     if (count > 1) {
@@ -1063,6 +1172,12 @@ cute_b200_status gemm_tn_multi(const cute_b200_gemm_desc &d, uint64_t a, uint64_
             if (!c_list[i] || ((c_list[i] ^ c_list[0]) & 31u) || (c_list[i] & mask))
                 return fail(CUTE_B200_ERR_MISALIGNED, "gemm_tn_multi: destination %d is null or aligned differently from the first", i);
     }
+    if (signal_list) {
+        if (d.k == 0) return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "gemm_tn_multi: the completion signal needs k > 0");
+        for (int i = 1; i < count; i++)
+            if (!signal_list[i] || (signal_list[i] & 3u))
+                return fail(CUTE_B200_ERR_MISALIGNED, "gemm_tn_multi: signal counter %d is null or not 4-byte aligned", i);
+    }
     cute_b200_gemm_desc dd = d;
     if (count > 1 && d.k == 0) {  // nothing to multiply: every destination is filled with zeros by its own launch
         for (int i = 0; i < count; i++) CB_TRY(gemm_tn(dd, a, b, c_list[i], stream, dev));
@@ -1074,6 +1189,7 @@ cute_b200_status gemm_tn_multi(const cute_b200_gemm_desc &d, uint64_t a, uint64_
     GemmExtras ex;
     ex.extra_c = c_list + 1;
     ex.extra_count = count - 1;
+    ex.signal = signal_list ? signal_list + 1 : nullptr;
     return gemm_tn_ex(dd, a, b, c_list[0], stream, dev, ex);
 }
 
@@ -1106,8 +1222,10 @@ static cute_b200_status gemm_tn_ex(const cute_b200_gemm_desc &d, uint64_t a, uin
         return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "gemm_tn: tile_n must be 0, 128 or 256, got %d", d.tile_n);
     if (d.cta_group < 0 || d.cta_group > 2)
         return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "gemm_tn: cta_group must be 0, 1 or 2, got %d", d.cta_group);
-    if (d.tile_m != 0 && d.tile_m != 128 && d.tile_m != 256)
-        return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "gemm_tn: tile_m must be 0, 128 or 256, got %d", d.tile_m);
+    if (d.tile_m != 0 && d.tile_m != 64 && d.tile_m != 128 && d.tile_m != 256)
+        return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "gemm_tn: tile_m must be 0, 64, 128 or 256, got %d", d.tile_m);
+    if (d.tile_m == 64 && d.cta_group == 1)
+        return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "gemm_tn: the 64-row tile needs a CTA pair (cta_group 0 or 2)");
     if (!c) return fail(CUTE_B200_ERR_NULL_POINTER, "gemm_tn: C is null");
     const bool c_bf16 = d.c_dtype == CUTE_B200_BF16;
     if (c & (c_bf16 ? 1u : 3u)) return fail(CUTE_B200_ERR_MISALIGNED, "gemm_tn: C is not aligned to its element size");
@@ -1127,7 +1245,7 @@ static cute_b200_status gemm_tn_ex(const cute_b200_gemm_desc &d, uint64_t a, uin
     if (d.split_k < 0 || d.split_k > 16)
         return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "gemm_tn: split_k must be 0 (choose) to 16, got %d", d.split_k);
     int group = 2, bn = 256, mh = 2, splits = 1;
-    choose_tiling(d.m, d.n, d.k, c_bf16 ? 2 : 4, dev.sm_count, d.cta_group, d.tile_n, d.tile_m / 128, d.split_k, 1, 16,
+    choose_tiling(d.m, d.n, d.k, c_bf16 ? 2 : 4, dev.sm_count, d.cta_group, d.tile_n, d.tile_m, d.split_k, 1, 16,
                   &group, &bn, &mh, &splits);
 
     GemmParams p = {};
@@ -1146,23 +1264,26 @@ static cute_b200_status gemm_tn_ex(const cute_b200_gemm_desc &d, uint64_t a, uin
     p.split_stride = 0;
     p.extra_count = ex.extra_count;
     for (int i = 0; i < ex.extra_count; i++) p.extra_c[i] = reinterpret_cast<void *>(ex.extra_c[i]);
+    if (ex.signal && ex.extra_count > 0) {
+        p.signal_count = ex.extra_count;
+        for (int i = 0; i < ex.extra_count; i++) p.signal[i] = reinterpret_cast<uint32_t *>(ex.signal[i]);
+        p.done_counter = dev.status_word + 8;  // words 8.. of the device's 64-byte status block are the library's own counters
+    }
     const size_t c_elem = c_bf16 ? 2 : 4;
     p.c_vec_ok = ((c & 15u) == 0 && (size_t(ldc) * c_elem) % 16 == 0) ? 1 : 0;
     if ((c & 31u) == 0 && (size_t(ldc) * c_elem) % 32 == 0) p.c_vec_ok = 2;
-    const uint32_t fmt = d.ab_dtype == CUTE_B200_BF16 ? 1u : 0u;
-    // Instruction descriptor: f32 accumulator, A and B format, both K-major,
-    // N >> 3 at bit 17, M >> 4 at bit 24 (M counts the rows of the whole pair).
-    p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(bn >> 3) << 17) | (uint32_t((BM * group) >> 4) << 24);
+    const int cta_rows = mh == 0 ? 64 : BM * mh;
+    p.idesc = make_idesc(d.ab_dtype == CUTE_B200_BF16, (mh == 0 ? 64 : BM) * group, bn);
 
     CUtensorMap tmA, tmB;
-    CB_TRY(make_tensor_map(&tmA, a, d.ab_dtype, d.m, d.k, BM * mh));
+    CB_TRY(make_tensor_map(&tmA, a, d.ab_dtype, d.m, d.k, cta_rows));
     CB_TRY(make_tensor_map(&tmB, b, d.ab_dtype, d.n, d.k, bn / group));
     // Several destinations: the pusher warp copies finished tiles by TMA when every C is 16-byte
     // aligned with a 16-byte row pitch; otherwise the epilogue stores to each of them from registers.
     CMaps tmC = {};
     if (p.extra_count > 0 && splits == 1 && ldc == d.n && (c & 15u) == 0 && (size_t(d.n) * c_elem) % 16 == 0 &&
         !(d.tuning[0] & 16)) {
-        const int box_rows = int(PUSH_BUF_BYTES) / (bn * int(c_elem));
+        const int box_rows = push_rows(bn, c_bf16);
         CB_TRY(make_tensor_map_c(&tmC.m[0], c, c_bf16, d.m, d.n, bn, box_rows));
         for (int i = 0; i < p.extra_count; i++)
             CB_TRY(make_tensor_map_c(&tmC.m[i + 1], reinterpret_cast<uint64_t>(p.extra_c[i]), c_bf16, d.m, d.n, bn, box_rows));
@@ -1203,7 +1324,45 @@ static cute_b200_status gemm_tn_ex(const cute_b200_gemm_desc &d, uint64_t a, uin
     if (group == G && bn == N_ && mh == H && c_bf16 == BF) return launch<G, N_, H, BF>(tmA, tmB, tmC, p, dev.sm_count, stream);
     CB_GEMM_VARIANTS(CB_CASE)
 #undef CB_CASE
-    return fail(CUTE_B200_ERR_UNSUPPORTED, "gemm_tn: no kernel for cta_group %d, tile %d x %d", group, BM * mh, bn);
+    return fail(CUTE_B200_ERR_UNSUPPORTED, "gemm_tn: no kernel for cta_group %d, tile %d x %d", group, cta_rows, bn);
+}
+
+template <int CTA_GROUP, int BN, int MH>
+static void fill_layout(bool ab_bf16, bool c_bf16, uint32_t smem_addr, cute_b200_gemm_layout *o) {
+    using C = Cfg<CTA_GROUP, BN, MH>;
+    o->instruction_descriptor = make_idesc(ab_bf16, C::UMMA_M, BN);
+    o->umma_m = C::UMMA_M, o->umma_n = BN, o->umma_k = UMMA_K;
+    o->block_k = BK;
+    o->cta_rows = C::A_ROWS;
+    o->a_stage_bytes = C::A_BYTES, o->b_stage_bytes = C::B_BYTES, o->stage_bytes = C::STAGE_BYTES, o->stages = C::STAGES;
+    o->accumulator_halves = C::HALVES, o->half_columns = C::HALF_COLS, o->accumulator_buffers = C::ACC_BUFS;
+    o->tmem_columns = C::TMEM_COLS;
+    o->threads = num_threads(BN, MH), o->epilogue_warps = 4 * epilogue_groups(BN, MH);
+    o->full_arrivals = C::FULL_ARRIVALS, o->empty_arrivals = C::EMPTY_ARRIVALS, o->tmem_full_arrivals = C::TFULL_ARRIVALS;
+    o->tmem_empty_arrivals = C::TEMPTY_ARRIVALS;
+    o->full_expect_tx_bytes = C::EXPECT_TX;
+    o->push_chunk_bytes = PUSH_BUF_BYTES, o->push_chunk_rows = push_rows(BN, c_bf16);
+    o->push_chunks_per_tile = C::A_ROWS / push_rows(BN, c_bf16);
+    o->shared_memory_bytes = C::SMEM_BYTES;
+    o->descriptor_k_step = DESC_K_STEP;
+    o->smem_descriptor = sw128_desc(smem_addr);
+}
+
+cute_b200_status gemm_layout_info(int cta_group, int tile_n, int tile_m, int ab_dtype, int c_dtype, uint32_t smem_addr,
+                                  cute_b200_gemm_layout *out) {
+    if (!out) return fail(CUTE_B200_ERR_NULL_POINTER, "gemm_layout_info: null output");
+    if ((ab_dtype != CUTE_B200_F16 && ab_dtype != CUTE_B200_BF16) || (c_dtype != CUTE_B200_F32 && c_dtype != CUTE_B200_BF16))
+        return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "gemm_layout_info: f16/bf16 inputs and f32/bf16 output only");
+    const int mh = tile_m == 64 ? 0 : tile_m / 128;
+    *out = cute_b200_gemm_layout{};
+#define CB_CASE(G, N_, H, BF)                                                                       \
+    if (cta_group == G && tile_n == N_ && mh == H && !BF && (tile_m == 64 || tile_m == 128 * H)) { \
+        fill_layout<G, N_, H>(ab_dtype == CUTE_B200_BF16, c_dtype == CUTE_B200_BF16, smem_addr, out); \
+        return CUTE_B200_OK;                                                                        \
+    }
+    CB_GEMM_VARIANTS(CB_CASE)
+#undef CB_CASE
+    return fail(CUTE_B200_ERR_UNSUPPORTED, "gemm_layout_info: no kernel for cta_group %d, tile %d x %d", cta_group, tile_m, tile_n);
 }
 
 }  // namespace cb

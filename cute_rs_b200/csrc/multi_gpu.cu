@@ -1,0 +1,470 @@
+// The launcher for several GPUs of one box, behind the C ABI: one process, one
+// host thread and one set of streams per GPU, peer access enabled between every
+// pair.  A large GEMM is cut into contiguous blocks of whole 128-row tiles of A
+// and C, one per GPU, with B whole in every GPU's memory; nothing crosses
+// between GPUs while the blocks are computed.  A caller that asks for a
+// replicated C gets it from the GEMM kernel itself (its pusher warp stores every
+// finished tile into the peers' C over NVLink) whenever the result qualifies,
+// else from an all-gather by the collective library (NCCL, loaded at run time
+// like the reference loads libcuda, src/cuda.rs:88-196) or, without it, from
+// device-to-device copies.  Peer memory is only ever the target of plain
+// stores and copies; no load reads it.
+//
+// The reference has one GPU and one entry, CudaContext::launch (src/cuda.rs:
+// 443-473): buffers in, a wait, buffers back.  cute_b200_gemm_tn_sharded keeps
+// that shape for device buffers, cute_b200_gemm_tn_sharded_host for host
+// buffers (every GPU uploads its rows of A and only its share of B, the shares
+// are exchanged over NVLink, and every GPU sends its rows of C back).
+#include <dlfcn.h>
+
+#include <chrono>
+#include <condition_variable>
+#include <cstring>
+#include <mutex>
+#include <thread>
+#include <vector>
+
+#include "common.cuh"
+
+namespace cb {
+namespace {
+
+constexpr uint32_t kCommMagic = 0xC0B200C0u;
+constexpr int kMaxGpus = 8;
+constexpr int kMaxPanels = 16;
+
+// The few entry points of the collective library that the fallback needs, resolved at run time.
+struct Nccl {
+    void *handle = nullptr;
+    int (*CommInitAll)(void **, int, const int *) = nullptr;
+    int (*CommDestroy)(void *) = nullptr;
+    int (*AllGather)(const void *, void *, size_t, int, void *, cudaStream_t) = nullptr;
+    int (*Broadcast)(const void *, void *, size_t, int, int, void *, cudaStream_t) = nullptr;
+    int (*GroupStart)() = nullptr;
+    int (*GroupEnd)() = nullptr;
+    const char *(*GetErrorString)(int) = nullptr;
+    bool load() {
+        if (handle) return true;
+        for (const char *name : {"libnccl.so.2", "libnccl.so"}) {
+            handle = dlopen(name, RTLD_NOW | RTLD_GLOBAL);
+            if (handle) break;
+        }
+        if (!handle) return false;
+        CommInitAll = reinterpret_cast<decltype(CommInitAll)>(dlsym(handle, "ncclCommInitAll"));
+        CommDestroy = reinterpret_cast<decltype(CommDestroy)>(dlsym(handle, "ncclCommDestroy"));
+        AllGather = reinterpret_cast<decltype(AllGather)>(dlsym(handle, "ncclAllGather"));
+        Broadcast = reinterpret_cast<decltype(Broadcast)>(dlsym(handle, "ncclBroadcast"));
+        GroupStart = reinterpret_cast<decltype(GroupStart)>(dlsym(handle, "ncclGroupStart"));
+        GroupEnd = reinterpret_cast<decltype(GroupEnd)>(dlsym(handle, "ncclGroupEnd"));
+        GetErrorString = reinterpret_cast<decltype(GetErrorString)>(dlsym(handle, "ncclGetErrorString"));
+        return CommInitAll && CommDestroy && AllGather && Broadcast && GroupStart && GroupEnd && GetErrorString;
+    }
+};
+constexpr int kNcclInt8 = 0;  // ncclInt8: the blocks travel as bytes, whatever C's type
+
+// Rendezvous of the per-GPU host threads of one call.  Every thread passes whether it is still
+// healthy; all of them learn whether everybody is, so that none waits for a thread that gave up.
+class HostBarrier {
+public:
+    void reset(int n) {
+        count_ = n, waiting_ = 0, generation_ = 0, all_ok_ = true, result_ = true;
+    }
+    bool arrive(bool ok) {
+        std::unique_lock<std::mutex> lock(mu_);
+        all_ok_ = all_ok_ && ok;
+        const uint64_t gen = generation_;
+        if (++waiting_ == count_) {
+            result_ = all_ok_;
+            waiting_ = 0;
+            generation_++;
+            cv_.notify_all();
+            return result_;
+        }
+        cv_.wait(lock, [&] { return generation_ != gen; });
+        return result_;
+    }
+
+private:
+    std::mutex mu_;
+    std::condition_variable cv_;
+    int count_ = 0, waiting_ = 0;
+    uint64_t generation_ = 0;
+    bool all_ok_ = true, result_ = true;
+};
+
+struct GpuState {
+    int ordinal = 0;
+    cudaStream_t compute = nullptr, up = nullptr, down = nullptr, spread[2] = {nullptr, nullptr};
+    cudaEvent_t b_up = nullptr, spread_join = nullptr, b_spread = nullptr, a_up[kMaxPanels] = {}, c_done[kMaxPanels] = {};
+    void *buf[3] = {nullptr, nullptr, nullptr};  // staging of the host-buffer call: A rows, B, C rows
+    size_t bytes[3] = {0, 0, 0};
+};
+
+struct Comm {
+    uint32_t magic = kCommMagic;
+    int n = 0;
+    bool distinct = true;   // no ordinal twice
+    bool peers_ok = true;   // every pair of different devices can reach each other's memory
+    GpuState gpu[kMaxGpus];
+    Nccl nccl;
+    bool nccl_tried = false, nccl_ok = false;
+    void *nccl_comm[kMaxGpus] = {};
+    HostBarrier barrier;
+    std::mutex call_mu;  // one call at a time per communicator
+};
+
+Comm *as_comm(void *p) {
+    Comm *c = static_cast<Comm *>(p);
+    return (c && c->magic == kCommMagic) ? c : nullptr;
+}
+
+struct Outcome {
+    cute_b200_status status = CUTE_B200_OK;
+    std::string message;
+};
+
+// Runs fn(g) on one host thread per GPU, that GPU current, and returns the first failure
+// (with its message moved into the caller's thread).
+template <class F>
+cute_b200_status on_every_gpu(Comm &comm, F &&fn) {
+    std::vector<Outcome> out(comm.n);
+    std::vector<std::thread> threads;
+    comm.barrier.reset(comm.n);
+    for (int g = 0; g < comm.n; g++)
+        threads.emplace_back([&, g] {
+            cudaError_t err = cudaSetDevice(comm.gpu[g].ordinal);
+            cute_b200_status st = err == cudaSuccess ? fn(g) : cuda_fail(err, "cudaSetDevice");
+            out[g].status = st;
+            if (st != CUTE_B200_OK) out[g].message = last_error();
+        });
+    for (auto &t : threads) t.join();
+    for (int g = 0; g < comm.n; g++)
+        if (out[g].status != CUTE_B200_OK) return fail(out[g].status, "GPU %d (device %d): %s", g, comm.gpu[g].ordinal, out[g].message.c_str());
+    return CUTE_B200_OK;
+}
+
+cute_b200_status ensure_nccl(Comm &comm) {
+    if (comm.nccl_tried) return comm.nccl_ok ? CUTE_B200_OK : fail(CUTE_B200_ERR_UNSUPPORTED, "the collective library is not available");
+    comm.nccl_tried = true;
+    if (!comm.distinct) return fail(CUTE_B200_ERR_UNSUPPORTED, "the collective library needs distinct devices");
+    if (!comm.nccl.load()) return fail(CUTE_B200_ERR_UNSUPPORTED, "libnccl.so.2 could not be loaded: %s", dlerror() ? dlerror() : "symbols missing");
+    int devs[kMaxGpus];
+    for (int g = 0; g < comm.n; g++) devs[g] = comm.gpu[g].ordinal;
+    const int rc = comm.nccl.CommInitAll(comm.nccl_comm, comm.n, devs);
+    if (rc != 0) return fail(CUTE_B200_ERR_CUDA, "ncclCommInitAll failed: %s", comm.nccl.GetErrorString(rc));
+    comm.nccl_ok = true;
+    return CUTE_B200_OK;
+}
+
+cute_b200_status grow(GpuState &gs, int slot, size_t bytes) {
+    if (gs.bytes[slot] >= bytes) return CUTE_B200_OK;
+    if (gs.buf[slot]) CB_CUDA(cudaFree(gs.buf[slot]));
+    gs.buf[slot] = nullptr;
+    gs.bytes[slot] = 0;
+    CB_CUDA(cudaMalloc(&gs.buf[slot], bytes ? bytes : 16));
+    gs.bytes[slot] = bytes;
+    return CUTE_B200_OK;
+}
+
+size_t c_elem_bytes(const cute_b200_gemm_desc &d) { return d.c_dtype == CUTE_B200_BF16 ? 2 : 4; }
+
+cute_b200_status check_desc(const cute_b200_gemm_desc *desc, const char *who) {
+    if (!desc) return fail(CUTE_B200_ERR_NULL_POINTER, "%s: desc is null", who);
+    if (desc->m <= 0 || desc->n <= 0 || desc->k < 0)
+        return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "%s: invalid size %dx%dx%d", who, desc->m, desc->n, desc->k);
+    if ((desc->ab_dtype != CUTE_B200_F16 && desc->ab_dtype != CUTE_B200_BF16) ||
+        (desc->c_dtype != CUTE_B200_F32 && desc->c_dtype != CUTE_B200_BF16))
+        return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "%s: f16/bf16 inputs and f32/bf16 output only", who);
+    return CUTE_B200_OK;
+}
+
+}  // namespace
+
+cute_b200_status comm_create(int ngpus, const int *ordinals, void **comm_out) {
+    if (!comm_out) return fail(CUTE_B200_ERR_NULL_POINTER, "comm_create: null output");
+    *comm_out = nullptr;
+    if (ngpus < 1 || ngpus > kMaxGpus)
+        return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "comm_create: 1 to %d GPUs, got %d", kMaxGpus, ngpus);
+    int count = 0;
+    cudaError_t err = cudaGetDeviceCount(&count);
+    if (err != cudaSuccess) {
+        cudaGetLastError();
+        return fail(CUTE_B200_ERR_NO_DEVICE, "cudaGetDeviceCount failed: %s", cudaGetErrorName(err));
+    }
+    Comm *comm = new Comm();
+    comm->n = ngpus;
+    for (int g = 0; g < ngpus; g++) {
+        const int ord = ordinals ? ordinals[g] : g;
+        if (ord < 0 || ord >= count) {
+            delete comm;
+            return fail(CUTE_B200_ERR_NO_DEVICE, "comm_create: device %d requested, %d present", ord, count);
+        }
+        comm->gpu[g].ordinal = ord;
+        for (int h = 0; h < g; h++)
+            if (comm->gpu[h].ordinal == ord) comm->distinct = false;
+    }
+    int previous = 0;
+    cudaGetDevice(&previous);
+    auto setup = [&]() -> cute_b200_status {
+        for (int g = 0; g < ngpus; g++) {
+            GpuState &gs = comm->gpu[g];
+            CB_TRY(cute_b200_init(gs.ordinal));  // selects the device
+            for (int h = 0; h < ngpus; h++) {
+                const int other = comm->gpu[h].ordinal;
+                if (other == gs.ordinal) continue;
+                int can = 0;
+                CB_CUDA(cudaDeviceCanAccessPeer(&can, gs.ordinal, other));
+                if (!can) {
+                    comm->peers_ok = false;
+                    continue;
+                }
+                err = cudaDeviceEnablePeerAccess(other, 0);
+                if (err == cudaErrorPeerAccessAlreadyEnabled) cudaGetLastError();
+                else if (err != cudaSuccess) return cuda_fail(err, "cudaDeviceEnablePeerAccess");
+            }
+            CB_CUDA(cudaStreamCreateWithFlags(&gs.compute, cudaStreamNonBlocking));
+            CB_CUDA(cudaStreamCreateWithFlags(&gs.up, cudaStreamNonBlocking));
+            CB_CUDA(cudaStreamCreateWithFlags(&gs.down, cudaStreamNonBlocking));
+            for (auto &s : gs.spread) CB_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+            CB_CUDA(cudaEventCreateWithFlags(&gs.b_up, cudaEventDisableTiming));
+            CB_CUDA(cudaEventCreateWithFlags(&gs.b_spread, cudaEventDisableTiming));
+            CB_CUDA(cudaEventCreateWithFlags(&gs.spread_join, cudaEventDisableTiming));
+            for (int i = 0; i < kMaxPanels; i++) {
+                CB_CUDA(cudaEventCreateWithFlags(&gs.a_up[i], cudaEventDisableTiming));
+                CB_CUDA(cudaEventCreateWithFlags(&gs.c_done[i], cudaEventDisableTiming));
+            }
+        }
+        return CUTE_B200_OK;
+    };
+    const cute_b200_status st = setup();
+    cudaSetDevice(previous);
+    if (st != CUTE_B200_OK) {
+        const std::string msg = last_error();
+        comm_destroy(comm);
+        return fail(st, "%s", msg.c_str());
+    }
+    *comm_out = comm;
+    return CUTE_B200_OK;
+}
+
+cute_b200_status comm_destroy(void *p) {
+    if (!p) return CUTE_B200_OK;
+    Comm *comm = as_comm(p);
+    if (!comm) return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "comm_destroy: not a communicator of this library");
+    int previous = 0;
+    cudaGetDevice(&previous);
+    for (int g = 0; g < comm->n; g++) {
+        GpuState &gs = comm->gpu[g];
+        if (cudaSetDevice(gs.ordinal) != cudaSuccess) continue;
+        cudaDeviceSynchronize();
+        if (comm->nccl_ok && comm->nccl_comm[g]) comm->nccl.CommDestroy(comm->nccl_comm[g]);
+        for (cudaStream_t s : {gs.compute, gs.up, gs.down, gs.spread[0], gs.spread[1]})
+            if (s) cudaStreamDestroy(s);
+        for (cudaEvent_t e : {gs.b_up, gs.b_spread, gs.spread_join})
+            if (e) cudaEventDestroy(e);
+        for (int i = 0; i < kMaxPanels; i++) {
+            if (gs.a_up[i]) cudaEventDestroy(gs.a_up[i]);
+            if (gs.c_done[i]) cudaEventDestroy(gs.c_done[i]);
+        }
+        for (void *b : gs.buf)
+            if (b) cudaFree(b);
+    }
+    cudaSetDevice(previous);
+    comm->magic = 0;
+    delete comm;
+    return CUTE_B200_OK;
+}
+
+cute_b200_status comm_info(void *p, int32_t out[4]) {
+    Comm *comm = as_comm(p);
+    if (!comm || !out) return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "comm_info: not a communicator of this library, or null output");
+    std::lock_guard<std::mutex> lock(comm->call_mu);
+    const bool nccl = ensure_nccl(*comm) == CUTE_B200_OK;
+    out[0] = comm->n, out[1] = comm->distinct ? 1 : 0, out[2] = comm->peers_ok ? 1 : 0, out[3] = nccl ? 1 : 0;
+    return CUTE_B200_OK;
+}
+
+cute_b200_status gemm_tn_sharded(void *p, const cute_b200_gemm_desc *desc, const uint64_t *dA_shard, const uint64_t *dB,
+                                 const uint64_t *dC, int replicate_c) {
+    Comm *comm = as_comm(p);
+    if (!comm) return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "gemm_tn_sharded: not a communicator of this library");
+    CB_TRY(check_desc(desc, "gemm_tn_sharded"));
+    if (!dA_shard || !dB || !dC) return fail(CUTE_B200_ERR_NULL_POINTER, "gemm_tn_sharded: null pointer list");
+    if (replicate_c < 0 || replicate_c > CUTE_B200_REPLICATE_COPIES)
+        return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "gemm_tn_sharded: replicate_c must be 0 to %d, got %d", CUTE_B200_REPLICATE_COPIES, replicate_c);
+    std::lock_guard<std::mutex> lock(comm->call_mu);
+    const int n = comm->n;
+    const size_t esize = c_elem_bytes(*desc), row_bytes = size_t(desc->n) * esize;
+    int begin[kMaxGpus], rows[kMaxGpus];
+    bool even = true;
+    for (int g = 0; g < n; g++) {
+        CB_TRY(cute_b200_shard_rows(desc->m, n, g, &begin[g], &rows[g]));
+        if (!dC[g] || (desc->k > 0 && rows[g] > 0 && (!dA_shard[g] || !dB[g])))
+            return fail(CUTE_B200_ERR_NULL_POINTER, "gemm_tn_sharded: null buffer for GPU %d", g);
+        if (rows[g] != rows[0]) even = false;
+    }
+    // How the blocks reach the other GPUs.
+    int how = replicate_c;
+    if (n == 1) how = CUTE_B200_REPLICATE_NONE;
+    const bool plain = desc->alpha == 1.0f && desc->beta == 0.0f;
+    const bool can_fuse = plain && desc->k > 0 && (comm->peers_ok || !comm->distinct);
+    if (how == CUTE_B200_REPLICATE_AUTO) {
+        bool tma_ok = row_bytes % 16 == 0;
+        for (int g = 0; g < n; g++) tma_ok = tma_ok && (dC[g] & 15u) == 0;
+        if (can_fuse && tma_ok) how = CUTE_B200_REPLICATE_FUSED;
+        else how = ensure_nccl(*comm) == CUTE_B200_OK ? CUTE_B200_REPLICATE_COLLECTIVE : CUTE_B200_REPLICATE_COPIES;
+    }
+    if (how == CUTE_B200_REPLICATE_FUSED && !can_fuse)
+        return fail(CUTE_B200_ERR_INVALID_ARGUMENT,
+                    "gemm_tn_sharded: the fused form needs alpha = 1, beta = 0, k > 0 and peer access between all GPUs");
+    if (how == CUTE_B200_REPLICATE_COLLECTIVE) CB_TRY(ensure_nccl(*comm));
+
+    return on_every_gpu(*comm, [&](int g) -> cute_b200_status {
+        GpuState &gs = comm->gpu[g];
+        DeviceState *dev;
+        CB_TRY(current_device(&dev));
+        cute_b200_gemm_desc d = *desc;
+        d.m = rows[g];
+        const uint64_t off = uint64_t(begin[g]) * row_bytes;
+        cute_b200_status st = CUTE_B200_OK;
+        if (how == CUTE_B200_REPLICATE_NONE) {
+            // replicate_c == 0: dC[g] is the block itself; a single GPU asked for a full C holds all of it anyway
+            if (rows[g] > 0) st = gemm_tn(d, dA_shard[g], dB[g], dC[g], gs.compute, *dev);
+        } else if (how == CUTE_B200_REPLICATE_FUSED) {
+            if (rows[g] > 0) {
+                uint64_t dests[kMaxGpus];
+                dests[0] = dC[g] + off;
+                for (int s = 1; s < n; s++) dests[s] = dC[(g + s) % n] + off;  // every link carries one peer's tiles
+                d.split_k = 1;
+                st = gemm_tn_multi(d, dA_shard[g], dB[g], dests, n, nullptr, gs.compute, *dev);
+            }
+        } else {
+            if (rows[g] > 0) st = gemm_tn(d, dA_shard[g], dB[g], dC[g] + off, gs.compute, *dev);
+            if (how == CUTE_B200_REPLICATE_COLLECTIVE) {
+                // Every thread has to join the collective, healthy or not, or the others would wait for it.
+                const Nccl &nc = comm->nccl;
+                int rc = 0;
+                if (even) {
+                    rc = nc.AllGather(reinterpret_cast<const void *>(dC[g] + off), reinterpret_cast<void *>(dC[g]),
+                                      size_t(rows[g]) * row_bytes, kNcclInt8, comm->nccl_comm[g], gs.compute);
+                } else {
+                    nc.GroupStart();
+                    for (int r = 0; r < n && rc == 0; r++)
+                        if (rows[r] > 0) {
+                            void *blk = reinterpret_cast<void *>(dC[g] + uint64_t(begin[r]) * row_bytes);
+                            rc = nc.Broadcast(blk, blk, size_t(rows[r]) * row_bytes, kNcclInt8, r, comm->nccl_comm[g], gs.compute);
+                        }
+                    const int rc2 = nc.GroupEnd();
+                    if (rc == 0) rc = rc2;
+                }
+                if (rc != 0 && st == CUTE_B200_OK) st = fail(CUTE_B200_ERR_CUDA, "the all-gather failed: %s", nc.GetErrorString(rc));
+            } else if (st == CUTE_B200_OK && rows[g] > 0) {
+                for (int s = 1; s < n; s++) {
+                    const int peer = (g + s) % n;
+                    CB_CUDA(cudaMemcpyPeerAsync(reinterpret_cast<void *>(dC[peer] + off), comm->gpu[peer].ordinal,
+                                                reinterpret_cast<const void *>(dC[g] + off), gs.ordinal,
+                                                size_t(rows[g]) * row_bytes, gs.compute));
+                }
+            }
+        }
+        // The call returns when every GPU's kernels, pushes and copies are complete: each thread
+        // waits for its device here and the caller joins all threads.
+        const cute_b200_status sync = sync_and_check();
+        return st != CUTE_B200_OK ? st : sync;
+    });
+}
+
+cute_b200_status gemm_tn_sharded_host(void *p, const cute_b200_gemm_desc *desc, const void *hA, const void *hB, void *hC,
+                                      double *seconds) {
+    Comm *comm = as_comm(p);
+    if (!comm) return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "gemm_tn_sharded_host: not a communicator of this library");
+    CB_TRY(check_desc(desc, "gemm_tn_sharded_host"));
+    if (!hC || (desc->k > 0 && (!hA || !hB))) return fail(CUTE_B200_ERR_NULL_POINTER, "gemm_tn_sharded_host: null buffer");
+    std::lock_guard<std::mutex> lock(comm->call_mu);
+    const auto t_start = std::chrono::steady_clock::now();
+    const int n = comm->n;
+    const size_t esize = c_elem_bytes(*desc), c_pitch = size_t(desc->n) * esize, k_bytes = size_t(desc->k) * 2;
+    const bool reads_c = !(desc->alpha == 1.0f && desc->beta == 0.0f);
+    int begin[kMaxGpus], rows[kMaxGpus], b_begin[kMaxGpus], b_rows[kMaxGpus];
+    for (int g = 0; g < n; g++) {
+        CB_TRY(cute_b200_shard_rows(desc->m, n, g, &begin[g], &rows[g]));
+        CB_TRY(cute_b200_shard_rows(desc->n, n, g, &b_begin[g], &b_rows[g]));  // the share of B this GPU uploads
+    }
+    const cute_b200_status st = on_every_gpu(*comm, [&](int g) -> cute_b200_status {
+        GpuState &gs = comm->gpu[g];
+        DeviceState *dev = nullptr;
+        // phase 1: staging memory, so that every GPU's B exists before anybody copies into it
+        cute_b200_status st = current_device(&dev);
+        if (st == CUTE_B200_OK) st = grow(gs, 0, size_t(rows[g]) * k_bytes);
+        if (st == CUTE_B200_OK) st = grow(gs, 1, size_t(desc->n) * k_bytes);
+        if (st == CUTE_B200_OK) st = grow(gs, 2, size_t(rows[g]) * c_pitch);
+        if (!comm->barrier.arrive(st == CUTE_B200_OK)) return st != CUTE_B200_OK ? st : fail(CUTE_B200_ERR_CUDA, "another GPU of the call failed");
+
+        // phase 2: this GPU's share of B goes up from the host and on to every other GPU over NVLink
+        char *dA = static_cast<char *>(gs.buf[0]), *dB = static_cast<char *>(gs.buf[1]), *dC = static_cast<char *>(gs.buf[2]);
+        auto phase2 = [&]() -> cute_b200_status {
+            if (desc->k > 0 && b_rows[g] > 0) {
+                const size_t off = size_t(b_begin[g]) * k_bytes, bytes = size_t(b_rows[g]) * k_bytes;
+                CB_CUDA(cudaMemcpyAsync(dB + off, static_cast<const char *>(hB) + off, bytes, cudaMemcpyHostToDevice, gs.up));
+                CB_CUDA(cudaEventRecord(gs.b_up, gs.up));
+                for (auto &s : gs.spread) CB_CUDA(cudaStreamWaitEvent(s, gs.b_up, 0));
+                for (int s = 1; s < n; s++) {  // two streams, so that two copy engines and two links work at a time
+                    const int peer = (g + s) % n;
+                    CB_CUDA(cudaMemcpyPeerAsync(static_cast<char *>(comm->gpu[peer].buf[1]) + off, comm->gpu[peer].ordinal,
+                                                dB + off, gs.ordinal, bytes, gs.spread[s & 1]));
+                }
+            }
+            // b_spread: this GPU's share of B is in its own memory and in every peer's
+            CB_CUDA(cudaEventRecord(gs.spread_join, gs.spread[0]));
+            CB_CUDA(cudaStreamWaitEvent(gs.spread[1], gs.spread_join, 0));
+            CB_CUDA(cudaEventRecord(gs.b_spread, gs.spread[1]));
+            return CUTE_B200_OK;
+        };
+        st = phase2();
+        if (!comm->barrier.arrive(st == CUTE_B200_OK)) {
+            cudaDeviceSynchronize();
+            return st != CUTE_B200_OK ? st : fail(CUTE_B200_ERR_CUDA, "another GPU of the call failed");
+        }
+
+        // phase 3: rows of A come up in panels; each panel is multiplied against all of B as soon as
+        // every share of B has landed here, and its rows of C go down while the next panel comes up
+        auto phase3 = [&]() -> cute_b200_status {
+            for (int peer = 0; peer < n; peer++) CB_CUDA(cudaStreamWaitEvent(gs.compute, comm->gpu[peer].b_spread, 0));
+            if (rows[g] == 0) return CUTE_B200_OK;
+            int panels = 8;
+            while (panels > 1 && (rows[g] / panels < 256 || size_t(rows[g] / panels) * c_pitch < (size_t(4) << 20))) panels /= 2;
+            const int per = ((rows[g] + panels - 1) / panels + 127) / 128 * 128;
+            int i = 0;
+            for (int r0 = 0; r0 < rows[g]; r0 += per, i++) {
+                const int r = rows[g] - r0 < per ? rows[g] - r0 : per;
+                const size_t grow0 = size_t(begin[g]) + r0;
+                if (desc->k > 0)
+                    CB_CUDA(cudaMemcpyAsync(dA + size_t(r0) * k_bytes, static_cast<const char *>(hA) + grow0 * k_bytes,
+                                            size_t(r) * k_bytes, cudaMemcpyHostToDevice, gs.up));
+                if (reads_c)
+                    CB_CUDA(cudaMemcpyAsync(dC + size_t(r0) * c_pitch, static_cast<const char *>(hC) + grow0 * c_pitch,
+                                            size_t(r) * c_pitch, cudaMemcpyHostToDevice, gs.up));
+                CB_CUDA(cudaEventRecord(gs.a_up[i], gs.up));
+                CB_CUDA(cudaStreamWaitEvent(gs.compute, gs.a_up[i], 0));
+                cute_b200_gemm_desc d = *desc;
+                d.m = r;
+                CB_TRY(gemm_tn(d, reinterpret_cast<uint64_t>(dA + size_t(r0) * k_bytes), reinterpret_cast<uint64_t>(dB),
+                               reinterpret_cast<uint64_t>(dC + size_t(r0) * c_pitch), gs.compute, *dev));
+                CB_CUDA(cudaEventRecord(gs.c_done[i], gs.compute));
+                CB_CUDA(cudaStreamWaitEvent(gs.down, gs.c_done[i], 0));
+                CB_CUDA(cudaMemcpyAsync(static_cast<char *>(hC) + grow0 * c_pitch, dC + size_t(r0) * c_pitch, size_t(r) * c_pitch,
+                                        cudaMemcpyDeviceToHost, gs.down));
+            }
+            return CUTE_B200_OK;
+        };
+        st = phase3();
+        const cute_b200_status sync = sync_and_check();  // everything queued reads or writes the caller's buffers
+        // nobody's B may be overwritten by the next call while a slower GPU still multiplies: leave together
+        comm->barrier.arrive(true);
+        return st != CUTE_B200_OK ? st : sync;
+    });
+    if (seconds) *seconds = std::chrono::duration<double>(std::chrono::steady_clock::now() - t_start).count();
+    return st;
+}
+
+}  // namespace cb

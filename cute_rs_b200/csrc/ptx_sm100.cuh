@@ -101,6 +101,15 @@ __device__ __forceinline__ uint32_t ld_acquire_shared(uint32_t addr) {
     asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
     return v;
 }
+// Counters that another GPU (or a later kernel) watches: add with release, read with acquire, system scope.
+__device__ __forceinline__ void red_release_sys_add(uint32_t *addr, uint32_t v) {
+    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *addr) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+    return v;
+}
 __device__ __forceinline__ void tma_store_2d(const void *tmap, uint32_t src, int32_t x, int32_t y) {
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
                      reinterpret_cast<uint64_t>(tmap)),

@@ -102,6 +102,11 @@ struct Api {
     decltype(&cute_b200_download) download = nullptr;
     decltype(&cute_b200_free) free_ = nullptr;
     decltype(&cute_b200_synchronize) synchronize = nullptr;
+    decltype(&cute_b200_comm_create) comm_create = nullptr;
+    decltype(&cute_b200_comm_destroy) comm_destroy = nullptr;
+    decltype(&cute_b200_comm_info) comm_info = nullptr;
+    decltype(&cute_b200_gemm_tn_sharded) gemm_tn_sharded = nullptr;
+    decltype(&cute_b200_gemm_tn_sharded_host) gemm_tn_sharded_host = nullptr;
 
     static const Api &get(const char *path = nullptr) {
         static Api api = load(path);
@@ -128,6 +133,11 @@ struct Api {
         bind(a.handle, a.download, "cute_b200_download");
         bind(a.handle, a.free_, "cute_b200_free");
         bind(a.handle, a.synchronize, "cute_b200_synchronize");
+        bind(a.handle, a.comm_create, "cute_b200_comm_create");
+        bind(a.handle, a.comm_destroy, "cute_b200_comm_destroy");
+        bind(a.handle, a.comm_info, "cute_b200_comm_info");
+        bind(a.handle, a.gemm_tn_sharded, "cute_b200_gemm_tn_sharded");
+        bind(a.handle, a.gemm_tn_sharded_host, "cute_b200_gemm_tn_sharded_host");
         return a;
     }
 };
@@ -202,6 +212,8 @@ struct KernelArg {
         for (size_t i = 0; i < v.size(); i++) h[i] = f32_to_bf16_bits(v[i]);
         return raw(DType::BF16, h.data(), h.size() * 2);
     }
+    // Elements of any type as raw bytes (KernelArg::Bytes, src/sim/mod.rs:80-84).
+    static KernelArg Bytes(DType t, const void *p, size_t nbytes) { return raw(t, p, nbytes); }
     static KernelArg ScalarF32(float x) {
         KernelArg a;
         a.dtype = DType::F32, a.is_scalar = true;
@@ -493,4 +505,44 @@ inline Kernel elementwise_add(bool tiled, int64_t m = 300, int64_t n = 512) {  /
 }
 
 }  // namespace examples
+// ---- several GPUs behind one call -------------------------------------------------------
+// What a `CudaContext` over all the GPUs of a box looks like: the launcher the library adds next
+// to src/cuda.rs.  One object, one call per GEMM; the library cuts the rows among the GPUs.
+class MultiGpuContext {
+   public:
+    explicit MultiGpuContext(const std::vector<int> &ordinals) {
+        std::vector<int32_t> o(ordinals.begin(), ordinals.end());
+        check(Api::get().comm_create(int32_t(o.size()), o.data(), &comm_));
+        n_ = int(o.size());
+    }
+    MultiGpuContext(const MultiGpuContext &) = delete;
+    MultiGpuContext &operator=(const MultiGpuContext &) = delete;
+    ~MultiGpuContext() {
+        if (comm_) Api::get().comm_destroy(comm_);
+    }
+    int gpus() const { return n_; }
+    bool has_collective_library() const {
+        int32_t out[4] = {0, 0, 0, 0};
+        check(Api::get().comm_info(comm_, out));
+        return out[3] != 0;
+    }
+    // Host matrices in, C back in place: CudaContext::launch for the row-sharded GEMM.
+    LaunchStats gemm(const cute_b200_gemm_desc &desc, const KernelArg &a, const KernelArg &b, KernelArg &c) const {
+        double seconds = 0.0;
+        check(Api::get().gemm_tn_sharded_host(comm_, &desc, a.bytes.data(), b.bytes.data(), c.bytes.data(), &seconds));
+        return {seconds};
+    }
+    // Device buffers, one per GPU (launch_on_device): returns when every GPU is done.
+    void gemm_on_devices(const cute_b200_gemm_desc &desc, const std::vector<uint64_t> &a_shards, const std::vector<uint64_t> &b,
+                         const std::vector<uint64_t> &c, int replicate_c) const {
+        if (int(a_shards.size()) != n_ || int(b.size()) != n_ || int(c.size()) != n_)
+            throw CudaError("one buffer per GPU is needed", CUTE_B200_ERR_INVALID_ARGUMENT);
+        check(Api::get().gemm_tn_sharded(comm_, &desc, a_shards.data(), b.data(), c.data(), replicate_c));
+    }
+
+   private:
+    void *comm_ = nullptr;
+    int n_ = 0;
+};
+
 }  // namespace cute

@@ -118,10 +118,18 @@ class PeerBuffer:
     must construct it at the same time.
     """
 
+    FLAG_BYTES = 256  # behind the data: counter r counts the launches of rank r that have landed here (launch_replicated_fused)
+
     def __init__(self, nbytes: int, world: int, rank: int, group=None):
+        import torch
         import torch.distributed as dist
         self.nbytes, self.world, self.rank = nbytes, world, rank
-        self.local = _lib.alloc(nbytes)
+        self.flag_offset = (nbytes + 255) // 256 * 256
+        self.local = _lib.alloc(self.flag_offset + self.FLAG_BYTES)
+        self.steps = 0  # signalled steps so far (every rank counts alike)
+        zeros = torch.zeros(self.FLAG_BYTES, dtype=torch.uint8, device="cuda")
+        _lib.copy_async(self.local + self.flag_offset, zeros.data_ptr(), self.FLAG_BYTES, torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
         handles = [None] * world
         dist.all_gather_object(handles, _lib.ipc_export(self.local), group=group)
         self.ptrs = [self.local if r == rank else _lib.ipc_open(handles[r]) for r in range(world)]
@@ -188,7 +196,8 @@ def launch_replicated_p2p(plan: RowShardedGemm, dA_shard: int, dB: int, peer_c: 
 
 
 def launch_replicated_fused(plan: RowShardedGemm, dA_shard: int, dB: int, peer_c: PeerBuffer, c_elem: int, group=None,
-                            tile_m: int = 0, register_stores: bool = False) -> None:
+                            tile_m: int = 0, register_stores: bool = False, barrier: str = "signal",
+                            timeout_ms: int = 30000) -> None:
     """C replicated on every GPU by the GEMM kernel itself: one launch that
     stores every finished tile into this rank's rows of its own C and then
     copies it, from inside the kernel, into the same rows of every peer's C
@@ -197,11 +206,17 @@ def launch_replicated_fused(plan: RowShardedGemm, dA_shard: int, dB: int, peer_c
     tensor cores work on the following tiles.  ``register_stores`` selects the
     fallback instead, 32-byte stores to every destination straight from the
     epilogue's registers, which NVLink carries far less well.  No collective
-    library moves data; a one-element all-reduce queued behind the kernel is
-    the closing barrier that tells every rank that all peers' stores into its C
-    have completed.  The plan's epilogue must be the
-    plain one (alpha 1, beta 0).  A rank without rows (more ranks than 128-row
-    tiles) launches nothing and only joins the barrier."""
+    library moves data.
+
+    How a rank learns that all peers' stores into its C have completed
+    (``barrier``): "signal" (default) - the last CTA of every rank's launch adds 1
+    to its own counter in each peer's memory, and a one-thread kernel queued behind
+    the GEMM waits, with a time limit, until the counters of all peers that have
+    rows have reached this step's number; no host synchronisation beyond the wait
+    for the stream and no collective call.  "all_reduce" - the earlier form, a
+    one-element NCCL all-reduce queued behind the kernel.  The plan's epilogue
+    must be the plain one (alpha 1, beta 0).  A rank without rows (more ranks
+    than 128-row tiles) launches nothing, sends no count and only waits."""
     import torch
     import torch.distributed as dist
     off = plan.row_begin * plan.n * c_elem
@@ -209,10 +224,20 @@ def launch_replicated_fused(plan: RowShardedGemm, dA_shard: int, dB: int, peer_c
     if not (plan.desc.alpha == 1.0 and plan.desc.beta == 0.0):
         raise ValueError("launch_replicated_fused needs alpha = 1, beta = 0")
     stream = torch.cuda.current_stream()
+    d = _lib.gemm_desc(max(plan.rows, 1), plan.n, plan.k, plan.desc.ab_dtype, plan.desc.c_dtype, tile_m=tile_m)
+    if register_stores:
+        d.tuning[0] |= 16
+    if barrier == "signal" and plan.k > 0:
+        order = [(plan.rank + s) % plan.world for s in range(plan.world)]
+        flags = [peer_c.ptrs[r] + peer_c.flag_offset + 4 * plan.rank for r in order]  # this rank's counter at every peer
+        if plan.rows > 0:
+            _lib.gemm_tn_multi_signal(d, dA_shard, dB, dests, flags, stream.cuda_stream)
+        peer_c.steps += 1
+        senders = sum(1 << r for r, (_, rows) in enumerate(plan.spans) if rows > 0 and r != plan.rank)
+        _lib.wait_signal(peer_c.local + peer_c.flag_offset, senders, peer_c.steps, timeout_ms, stream.cuda_stream)
+        stream.synchronize()
+        return
     if plan.rows > 0:
-        d = _lib.gemm_desc(plan.rows, plan.n, plan.k, plan.desc.ab_dtype, plan.desc.c_dtype, tile_m=tile_m)
-        if register_stores:
-            d.tuning[0] |= 16
         _lib.gemm_tn_multi(d, dA_shard, dB, dests, stream.cuda_stream)
     # A one-element all-reduce queued behind the kernel is the barrier: it cannot finish on any rank
     # before every rank has joined it, which each does only after its own pushes have completed.

@@ -91,7 +91,8 @@ typedef struct {
     float alpha, beta;
     int32_t tile_n;    /* columns of C per tile: 0 = choose; 128 or 256 */
     int32_t cta_group; /* 0 = choose; 1 = one CTA per tile; 2 = a CTA pair shares each tile's MMAs */
-    int32_t tile_m;    /* rows of C per CTA: 0 = choose; 128 or 256 */
+    int32_t tile_m;    /* rows of C per CTA: 0 = choose; 128 or 256; 64 = the pair tile for few row tiles and a long
+                          k (needs cta_group 0 or 2): 16 KiB stages, a 12-deep ring */
     int32_t split_k;   /* k ranges computed as separate work units and summed in ascending order by a second kernel
                           through an f32 scratch buffer the library allocates on first need: 0 = choose, 1 = never,
                           2..16 = exactly that many (cut down to the number of 64-wide k blocks when k is shorter;
@@ -259,12 +260,135 @@ cute_b200_status cute_b200_copy_async(uint64_t dst, uint64_t src, uint64_t bytes
 cute_b200_status cute_b200_gemm_tn_multi(const cute_b200_gemm_desc *desc, uint64_t dA, uint64_t dB,
                                          const uint64_t *dC_list, int32_t count, void *stream);
 
+/* The same with a completion signal in place of a barrier among the processes.
+ * dSignal_list[i], i >= 1, is the address (as this process sees it, e.g. a
+ * cute_b200_ipc_open mapping) of a 32-bit counter in the memory of the GPU
+ * that owns dC_list[i]; entry 0 is ignored.  When every CTA of the launch has
+ * finished - all stores to the first C and all stores to every other
+ * destination complete - the last CTA adds 1 to each counter (release, system
+ * scope).  The owner of a destination learns that its copy of these rows is
+ * complete by waiting for its counters: cute_b200_wait_signal queues a
+ * one-thread kernel on `stream` that polls the 32-bit counters dSignals[i]
+ * for every bit i set in `mask` (acquire, system scope) until each has reached
+ * `at_least` (compared as wrapping counts) or `timeout_ms` has passed; running
+ * out is reported like every other bounded wait ({7, at_least, index of the
+ * counter that was short, its value} in cute_b200_device_status,
+ * CUTE_B200_ERR_DEVICE_TIMEOUT from cute_b200_synchronize), and the device
+ * stays usable.  The intended use is one counter per sender in every
+ * receiver's memory, each growing by one per step, so that a sender that runs
+ * a step ahead cannot be mistaken for one that is a step behind.  Counters are
+ * never reset by the library; the caller zeroes them once (cute_b200_alloc
+ * does not).  k must be positive; one signalling launch at a time per device
+ * (they share the device's count of finished CTAs).  No host synchronisation
+ * and no collective call is needed on the step.  No counterpart in the
+ * reference. */
+cute_b200_status cute_b200_gemm_tn_multi_signal(const cute_b200_gemm_desc *desc, uint64_t dA, uint64_t dB,
+                                                const uint64_t *dC_list, const uint64_t *dSignal_list, int32_t count,
+                                                void *stream);
+cute_b200_status cute_b200_wait_signal(uint64_t dSignals, uint32_t mask, uint32_t at_least, uint32_t timeout_ms,
+                                       void *stream);
+
+/* ---- one call for all the GPUs of a box -------------------------------------
+ * The launcher next to CudaContext::launch (src/cuda.rs:443-473) for a GEMM too
+ * large, or too urgent, for one GPU: ONE process drives `ngpus` devices, one
+ * host thread and one set of streams each, with peer access enabled between
+ * every pair.  GPU g of the communicator owns the row block
+ * cute_b200_shard_rows(desc->m, ngpus, g) of A and C; B is whole in every
+ * GPU's memory; no data crosses between GPUs while the blocks are computed.
+ * Both calls return when every GPU has finished (like launch: buffers in, a
+ * wait, buffers back), with the first failure of any GPU as the status and its
+ * message in cute_b200_last_error ("GPU 3 (device 3): ...", worded like
+ * src/cuda.rs:532-546).  One call at a time per communicator; the reference has
+ * no multi-GPU path, this extends its launcher.
+ *
+ * cute_b200_comm_create: `ordinals` NULL means devices 0 .. ngpus-1; at most 8.
+ * A device may be named more than once (its blocks are then computed one after
+ * the other on that device; useful to run a partition meant for more GPUs than
+ * are present).  cute_b200_comm_info: out = {ngpus, all devices distinct, peer
+ * access between every pair, collective library usable}.
+ *
+ * cute_b200_gemm_tn_sharded (device buffers, one pointer per GPU, each in that
+ * GPU's memory): dA_shard[g] = GPU g's rows of A, dB[g] = all of B.  With
+ * replicate_c == CUTE_B200_REPLICATE_NONE, dC[g] is GPU g's row block of C.
+ * Otherwise dC[g] is a FULL (m, n) C on GPU g and every GPU ends up with all
+ * of it:
+ *   CUTE_B200_REPLICATE_FUSED       the GEMM kernel's pusher warp stores each
+ *       finished tile into the peers' C over NVLink while the tensor cores go
+ *       on (cute_b200_gemm_tn_multi); needs alpha 1, beta 0, peer access;
+ *   CUTE_B200_REPLICATE_COLLECTIVE  GEMM into the own block, then ncclAllGather
+ *       (ncclBroadcast per block when the blocks are uneven); NCCL is loaded
+ *       with dlopen("libnccl.so.2") on first need, as the reference loads
+ *       libcuda (src/cuda.rs:88-196);
+ *   CUTE_B200_REPLICATE_COPIES      GEMM, then one device-to-device copy of the
+ *       block per peer;
+ *   CUTE_B200_REPLICATE_AUTO        FUSED when it applies and every C takes the
+ *       TMA stores (16-byte aligned base and row pitch), else COLLECTIVE when
+ *       NCCL is there, else COPIES.
+ *
+ * cute_b200_gemm_tn_sharded_host (host buffers, the convention of
+ * CudaContext::launch): hA (m, k), hB (n, k) and hC (m, n) are whole matrices
+ * in host memory (pinned memory makes the copies faster).  Every GPU uploads
+ * its rows of A and only its 1/ngpus share of B's rows; the shares are passed
+ * on to the other GPUs by device-to-device copies over NVLink while A's panels
+ * come up; each panel of rows is multiplied as soon as B is complete and its
+ * rows of C go back to hC while the next panel is on its way.  hC is read
+ * first only when beta != 0.  Staging memory is kept by the communicator.
+ * `seconds`, if not NULL, receives the duration of the call. */
+enum {
+    CUTE_B200_REPLICATE_NONE = 0,
+    CUTE_B200_REPLICATE_AUTO = 1,
+    CUTE_B200_REPLICATE_FUSED = 2,
+    CUTE_B200_REPLICATE_COLLECTIVE = 3,
+    CUTE_B200_REPLICATE_COPIES = 4
+};
+cute_b200_status cute_b200_comm_create(int32_t ngpus, const int32_t *ordinals, void **comm_out);
+cute_b200_status cute_b200_comm_destroy(void *comm);
+cute_b200_status cute_b200_comm_info(void *comm, int32_t out[4]);
+cute_b200_status cute_b200_gemm_tn_sharded(void *comm, const cute_b200_gemm_desc *desc, const uint64_t *dA_shard,
+                                           const uint64_t *dB, const uint64_t *dC, int32_t replicate_c);
+cute_b200_status cute_b200_gemm_tn_sharded_host(void *comm, const cute_b200_gemm_desc *desc, const void *hA, const void *hB,
+                                                void *hC, double *seconds);
+
 /* ---- bounded waits ----------------------------------------------------------
  * Every spin on an mbarrier inside the GEMM kernel has a time limit.  A CTA
  * that gives up records {code, role/stage, block index, parity} here and the
  * kernel drains and returns instead of hanging.  Reads and clears the word
  * of the current device (synchronises the device).  out[0] == 0: no report. */
 cute_b200_status cute_b200_device_status(uint32_t out[4]);
+
+/* ---- what the compiled GEMM kernel is built from ------------------------------
+ * The constants of one tiling (cta_group 1 or 2, tile_n 128 or 256, tile_m 64,
+ * 128 or 256, the operand and result types), produced by the very expressions
+ * the kernel is compiled from: the tcgen05.mma instruction descriptor, the
+ * shared-memory matrix descriptor of a 128-byte-swizzled tile at `smem_addr`,
+ * the bytes and depth of the TMA ring, the accumulators' place in TMEM, the
+ * arrival and transaction counts of the pipeline's mbarriers and the pusher's
+ * chunk shape.  Host arithmetic only (works without a GPU).  It lets the
+ * Sm100 atoms (the form in which src/atom would describe this kernel, cf.
+ * src/atom/mma.rs:148-198, src/atom/copy.rs:46-90) and the protocol checker be
+ * held against the kernel as it is built rather than against a copy of its
+ * numbers.  No counterpart in the reference. */
+typedef struct {
+    uint32_t instruction_descriptor;
+    uint32_t umma_m, umma_n, umma_k; /* shape of one tcgen05.mma over the CTA group */
+    uint32_t block_k;                /* k per ring stage */
+    uint32_t cta_rows;               /* rows of C per CTA */
+    uint32_t a_stage_bytes, b_stage_bytes, stage_bytes, stages;
+    uint32_t accumulator_halves;     /* 128-lane accumulators per CTA */
+    uint32_t half_columns;           /* TMEM columns of one of them */
+    uint32_t accumulator_buffers;    /* 2 = the epilogue overlaps the next tile's main loop */
+    uint32_t tmem_columns;           /* allocated */
+    uint32_t threads, epilogue_warps;
+    uint32_t full_arrivals, empty_arrivals, tmem_full_arrivals, tmem_empty_arrivals;
+    uint32_t full_expect_tx_bytes;   /* announced per stage on the (leader's) full barrier */
+    uint32_t push_chunk_bytes, push_chunk_rows, push_chunks_per_tile;
+    uint32_t shared_memory_bytes;
+    uint32_t descriptor_k_step;      /* added to a descriptor's address field per umma_k */
+    uint64_t smem_descriptor;
+} cute_b200_gemm_layout;
+
+cute_b200_status cute_b200_gemm_layout_info(int32_t cta_group, int32_t tile_n, int32_t tile_m, int32_t ab_dtype,
+                                            int32_t c_dtype, uint32_t smem_addr, cute_b200_gemm_layout *out);
 
 /* Number of kernels this library has launched from the calling process. */
 uint64_t cute_b200_launch_count(void);

@@ -221,11 +221,69 @@ static void gpu_checks() {
     }
 }
 
+// The launcher for several GPUs: one call, host matrices in, C back; rows cut among the GPUs of
+// the communicator.  {0, 0} runs a two-GPU partition on one device; {0, 1} needs a second GPU and
+// is skipped without one.  Integer data: bit-exact against the oracle.
+static void multi_gpu_checks() {
+    const size_t m = 1000, n = 264, k = 136;
+    Lcg g;
+    std::vector<uint16_t> a(m * k), b(n * k);
+    for (auto &x : a) x = f32_to_bf16_bits(float(int(g.next() % 17) - 8));
+    for (auto &x : b) x = f32_to_bf16_bits(float(int(g.next() % 17) - 8));
+    std::vector<float> sim(m * n);
+    oracle_gemm_tn(1, 2, m, n, k, a.data(), b.data(), sim.data(), 1.0f, 0.0f, 0, m);
+    cute_b200_gemm_desc d = {};
+    d.m = int(m), d.n = int(n), d.k = int(k), d.ab_dtype = CUTE_B200_BF16, d.c_dtype = CUTE_B200_F32, d.alpha = 1.0f;
+    const KernelArg ka = KernelArg::Bytes(DType::BF16, a.data(), a.size() * 2), kb = KernelArg::Bytes(DType::BF16, b.data(), b.size() * 2);
+    for (const std::vector<int> &devices : {std::vector<int>{0, 0}, std::vector<int>{0, 1}, std::vector<int>{0, 0, 0}}) {
+        try {
+            MultiGpuContext ctx(devices);
+            KernelArg kc = KernelArg::f32(std::vector<float>(m * n, -1.0f));
+            const LaunchStats stats = ctx.gemm(d, ka, kb, kc);
+            EXPECT(stats.kernel_seconds > 0.0);
+            EXPECT(std::memcmp(kc.bytes.data(), sim.data(), sim.size() * 4) == 0);
+            // device buffers, C replicated by the kernel's own stores: both copies hold every row
+            CudaContext first(devices[0]);
+            std::vector<DeviceBuffer> keep;
+            std::vector<uint64_t> pa, pb, pc;
+            for (size_t i = 0; i < devices.size(); i++) {
+                CudaContext here(devices[i]);
+                const size_t tiles = (m + 127) / 128, base = tiles / devices.size(), extra = tiles % devices.size();
+                const size_t t0 = i * base + (i < extra ? i : extra), t1 = t0 + base + (i < extra ? 1 : 0);
+                const size_t lo = std::min(t0 * 128, m), hi = std::min(t1 * 128, m);
+                keep.push_back(here.upload(KernelArg::Bytes(DType::BF16, a.data() + lo * k, std::max<size_t>(hi - lo, 1) * k * 2)));
+                pa.push_back(keep.back().ptr());
+                keep.push_back(here.upload(kb));
+                pb.push_back(keep.back().ptr());
+                keep.push_back(here.upload(KernelArg::f32(std::vector<float>(m * n, 0.0f))));
+                pc.push_back(keep.back().ptr());
+            }
+            ctx.gemm_on_devices(d, pa, pb, pc, CUTE_B200_REPLICATE_AUTO);
+            for (size_t i = 0; i < devices.size(); i++) {
+                CudaContext here(devices[i]);
+                KernelArg back = KernelArg::f32(std::vector<float>(m * n, -1.0f));
+                here.download(keep[3 * i + 2], back);
+                EXPECT(std::memcmp(back.bytes.data(), sim.data(), sim.size() * 4) == 0);
+            }
+        } catch (const CudaError &e) {
+            if (e.status == CUTE_B200_ERR_NO_DEVICE && devices.size() == 2 && devices[1] == 1) {
+                std::printf("skipped {0, 1}: %s\n", e.message.c_str());
+                continue;
+            }
+            throw;
+        }
+    }
+    EXPECT(error_of([] { MultiGpuContext none(std::vector<int>{}); }) == "comm_create: 1 to 8 GPUs, got 0");
+}
+
 int main(int argc, char **argv) {
     const std::string mode = argc > 1 ? argv[1] : "cpu";
     try {
         cpu_checks();
-        if (mode == "gpu") gpu_checks();
+        if (mode == "gpu") {
+            gpu_checks();
+            multi_gpu_checks();
+        }
     } catch (const std::exception &e) {
         std::printf("FAIL: exception: %s\n", e.what());
         return 2;

@@ -191,14 +191,57 @@ def test_tiled_mma_matches_the_restated_reference_kernel():
     assert len(owned) == len(set(owned)) == 128 * 128
 
 
+def test_sm100_atoms_match_the_compiled_kernel(lib):
+    """The atoms against the library's own account of every tiling it instantiates
+    (cute_b200_gemm_layout_info evaluates the expressions the kernel is compiled from):
+    instruction descriptor, shared-memory descriptor and its k step, TMA box bytes, the
+    ring that fits, TMEM columns, the pusher's chunk."""
+    for g, tile_n, tile_m in lib.GEMM_TILINGS:
+        for ab, dt in ((lib.F16, DType.F16), (lib.BF16, DType.BF16)):
+            for cdt, c_bytes in ((lib.F32, 4), (lib.BF16, 2)):
+                info = lib.gemm_layout_info(g, tile_n, tile_m, ab, cdt, smem_addr=0x4400)
+                op = Sm100UmmaOp(dt, min(tile_m, 128) * g, tile_n, cta_group=g)
+                assert info.instruction_descriptor == op.instruction_descriptor(), (g, tile_n, tile_m)
+                assert (info.umma_m, info.umma_n, info.umma_k) == (op.m, op.n, op.shape_k)
+                assert info.smem_descriptor == sw128_descriptor(0x4400)
+                assert sw128_descriptor(0x4400 + 2 * info.umma_k) - sw128_descriptor(0x4400) == info.descriptor_k_step
+                # one stage = the A box and this CTA's share of the B box, 64 k each (one 128-byte swizzle row)
+                assert info.block_k * 2 == CopyOp.TmaLoad(rows=1).swizzle_bytes
+                assert info.a_stage_bytes == CopyOp.TmaLoad(rows=info.cta_rows).box_bytes
+                assert info.b_stage_bytes == CopyOp.TmaLoad(rows=tile_n // g).box_bytes
+                assert info.stage_bytes == info.a_stage_bytes + info.b_stage_bytes
+                assert info.full_expect_tx_bytes == g * info.stage_bytes
+                assert info.stages == min(192 * 1024 // info.stage_bytes, 12) and info.stages * info.stage_bytes <= 192 * 1024
+                assert info.cta_rows == tile_m and info.accumulator_halves == max(tile_m // 128, 1)
+                assert info.half_columns == op.tmem_columns
+                cols = info.accumulator_halves * info.half_columns * info.accumulator_buffers
+                assert cols <= info.tmem_columns <= 512 and info.tmem_columns in (128, 256, 512)
+                assert info.accumulator_buffers == (2 if 2 * info.accumulator_halves * info.half_columns <= 512 else 1)
+                # the last accumulator element sits inside the allocation
+                cta, lane, col = op.tmem_coord(op.m - 1, op.n - 1, column0=(info.accumulator_halves - 1) * info.half_columns)
+                assert cta == g - 1 and lane == 127 and col < info.tmem_columns
+                # the epilogue warps cover the 128 lanes; one TMEM read is 32 lanes x 32 columns
+                assert info.epilogue_warps % 4 == 0 and info.threads == 32 * (2 + info.epilogue_warps + 1)
+                assert info.half_columns % (CopyOp.TmemLoad().columns * (info.epilogue_warps // 4)) == 0
+                store = CopyOp.TmaStore(rows=info.push_chunk_rows, cols=tile_n, elem_bytes=c_bytes)
+                assert store.box_bytes == info.push_chunk_bytes == 16384
+                assert info.push_chunks_per_tile * info.push_chunk_rows == info.cta_rows
+                assert info.shared_memory_bytes <= 227 * 1024
+    with pytest.raises(lib.CuteB200Error):
+        lib.gemm_layout_info(1, 128, 64)  # the 64-row tile is a pair tile
+
+
 def test_sm100_umma_atom():
     op = Sm100UmmaOp(DType.BF16, 256, 256, cta_group=2)
     assert op.instruction_descriptor() == 0x10400490
+    half = Sm100UmmaOp(DType.BF16, 128, 128, cta_group=2)  # 64 rows per CTA
+    assert (half.rows_per_cta, half.tmem_columns) == (64, 64)
+    assert half.tmem_coord(70, 5) == (1, 6, 5) and half.tmem_coord(70, 64 + 5, column0=64) == (1, 64 + 6, 64 + 5)
     assert Sm100UmmaOp(DType.F16, 128, 128).instruction_descriptor() == (1 << 4) | (16 << 17) | (8 << 24)
     assert op.tmem_coord(130, 17, column0=256) == (1, 2, 273)
     assert make_mma_atom(op).shape_mnk == (256, 256, 16)
     with pytest.raises(ValueError):
-        Sm100UmmaOp(DType.BF16, 128, 256, cta_group=2)
+        Sm100UmmaOp(DType.BF16, 256, 256, cta_group=1)
     with pytest.raises(ValueError):
         Sm100UmmaOp(DType.BF16, 128, 264)
 

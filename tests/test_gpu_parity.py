@@ -227,7 +227,8 @@ GEMM_SHAPES = [(128, 128, 64), (256, 128, 96), (128, 256, 160), (256, 256, 256),
 @pytest.mark.parametrize("m,n,k", GEMM_SHAPES)
 @pytest.mark.parametrize("ab_name", ["f16", "bf16"])
 @pytest.mark.parametrize("cta_group,tile_n,tile_m", [(1, 128, 128), (1, 256, 128), (2, 128, 128), (2, 256, 128), (1, 128, 256),
-                                                      (1, 256, 256), (2, 128, 256), (2, 256, 256), (0, 0, 0)])
+                                                      (1, 256, 256), (2, 128, 256), (2, 256, 256), (0, 0, 0),
+                                                      (2, 128, 64), (2, 256, 64), (0, 0, 64)])
 def test_gemm_small_integers_bit_exact(lib, gpu, m, n, k, ab_name, cta_group, tile_n, tile_m):
     ab = lib.F16 if ab_name == "f16" else lib.BF16
     a, b, _ = lcg_buffers([m * k, n * k, 0], small=True)
@@ -250,7 +251,7 @@ def test_gemm_example_inputs_match_golden(lib, gpu, golden, shape, ab_name):
 
 @pytest.mark.parametrize("m,n,k", [(256, 128, 96), (256, 256, 256), (512, 384, 2048)])
 @pytest.mark.parametrize("ab_name", ["f16", "bf16"])
-@pytest.mark.parametrize("cta_group,tile_m", [(1, 128), (2, 128), (2, 256)])
+@pytest.mark.parametrize("cta_group,tile_m", [(1, 128), (2, 128), (2, 256), (2, 64)])
 def test_gemm_random_within_reference_bound(lib, gpu, m, n, k, ab_name, cta_group, tile_m):
     ab = lib.F16 if ab_name == "f16" else lib.BF16
     a, b, _ = lcg_buffers([m * k, n * k, 0], small=False)
@@ -273,7 +274,7 @@ def test_gemm_config0_256_cubed_uniform_seed0(lib, gpu):
 
 @pytest.mark.parametrize("m,n,k", [(1, 1, 8), (100, 200, 72), (200, 136, 8), (129, 257, 520), (300, 520, 200), (128, 130, 64)])
 @pytest.mark.parametrize("cdt_name", ["f32", "bf16"])
-@pytest.mark.parametrize("cta_group,tile_m", [(1, 128), (2, 128), (2, 256), (1, 256)])
+@pytest.mark.parametrize("cta_group,tile_m", [(1, 128), (2, 128), (2, 256), (1, 256), (2, 64), (0, 64)])
 def test_gemm_ragged_shapes(lib, gpu, m, n, k, cdt_name, cta_group, tile_m):
     cdt = lib.F32 if cdt_name == "f32" else lib.BF16
     a, b, _ = lcg_buffers([m * k, n * k, 0], small=True)
@@ -289,7 +290,7 @@ def test_gemm_ragged_shapes(lib, gpu, m, n, k, cdt_name, cta_group, tile_m):
 @pytest.mark.parametrize("m,n,k", [(1, 8, 8), (100, 200, 72), (200, 136, 8), (129, 257, 520), (300, 520, 200), (128, 130, 64),
                                    (512, 384, 1088), (64, 64, 0)])
 @pytest.mark.parametrize("cdt_name", ["f32", "bf16"])
-@pytest.mark.parametrize("cta_group,tile_m", [(0, 0), (1, 128), (2, 128), (2, 256)])
+@pytest.mark.parametrize("cta_group,tile_m", [(0, 0), (1, 128), (2, 128), (2, 256), (2, 64)])
 @pytest.mark.parametrize("register_stores", [False, True])
 def test_gemm_several_destinations(lib, gpu, m, n, k, cdt_name, cta_group, tile_m, register_stores):
     """gemm_tn_multi writes the same C to every destination, by TMA stores where the
@@ -407,7 +408,7 @@ def test_gemm_random_shapes_and_tilings(lib, gpu, seed):
 
 @pytest.mark.parametrize("cdt_name", ["f32", "bf16"])
 @pytest.mark.parametrize("alpha,beta", [(1.5, -0.5), (0.0, 1.0), (2.0, 0.0), (1.0, 1.0)])
-@pytest.mark.parametrize("tile_m", [128, 256])
+@pytest.mark.parametrize("tile_m", [64, 128, 256])
 def test_gemm_alpha_beta_epilogue(lib, gpu, cdt_name, alpha, beta, tile_m):
     cdt = lib.F32 if cdt_name == "f32" else lib.BF16
     m, n, k = 256, 384, 128
@@ -437,6 +438,35 @@ def test_gemm_split_k(lib, gpu, m, n, k, split_k, cdt_name, alpha, beta):
     got = run_gemm(lib, a_bits, b_bits, lib.F16, cdt, alpha, beta, c0=c0, split_k=split_k)
     want = oracle.gemm_tn(a_bits, b_bits, lib.F16, cdt, alpha, beta, c_init=c0)
     assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("seed", range(3))
+def test_gemm_64_row_tile_random_shapes(lib, gpu, seed):
+    """The 64-rows-per-CTA pair tile (tile_m = 64) over random ragged sizes, both column
+    widths, input and output types, k splits and epilogues; integer data, bit-exact."""
+    rng = np.random.default_rng(6400 + seed)
+    for _ in range(10):
+        m, n = int(rng.integers(1, 700)), int(rng.integers(1, 700))
+        k = 8 * int(rng.integers(1, 260))
+        ab = lib.F16 if rng.integers(2) else lib.BF16
+        cdt = lib.F32 if rng.integers(2) else lib.BF16
+        tile_n, cta_group = int(rng.choice([0, 128, 256])), int(rng.choice([0, 2]))
+        split_k = int(rng.choice([0, 1, 1, 2, 3]))
+        alpha, beta = [(1.0, 0.0), (1.0, 0.0), (2.0, 0.0), (1.0, 1.0), (0.5, -1.0)][int(rng.integers(5))]
+        a_bits = conv(lib, ab)(rng.integers(-4, 5, (m, k)).astype(np.float32))
+        b_bits = conv(lib, ab)(rng.integers(-4, 5, (n, k)).astype(np.float32))
+        c0f = rng.integers(-8, 9, (m, n)).astype(np.float32)
+        c0 = c0f if cdt == lib.F32 else oracle.f32_to_bf16_bits(c0f)
+        got = run_gemm(lib, a_bits, b_bits, ab, cdt, alpha, beta, c0=c0.copy(), tile_n=tile_n, cta_group=cta_group, tile_m=64,
+                       split_k=split_k)
+        want = oracle.gemm_tn(a_bits, b_bits, ab, cdt, alpha, beta, c_init=c0)
+        assert np.array_equal(got, want), (m, n, k, ab, cdt, cta_group, tile_n, split_k, alpha, beta)
+
+
+def test_gemm_64_row_tile_needs_a_pair(lib, gpu):
+    with pytest.raises(lib.CuteB200Error) as e:
+        lib.gemm_tn(lib.gemm_desc(128, 128, 64, lib.F16, lib.F32, cta_group=1, tile_m=64), 256, 256, 256, 0)
+    assert e.value.status == lib.ERR_INVALID_ARGUMENT and "CTA pair" in e.value.message
 
 
 def test_gemm_split_k_random_within_bound(lib, gpu):

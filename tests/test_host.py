@@ -54,6 +54,31 @@ def test_no_cpu_fallback_without_a_device(lib):
         CudaContext.new(0)
 
 
+def test_sharded_launcher_checks_its_arguments_without_a_device(lib):
+    import ctypes
+    with pytest.raises(lib.CuteB200Error) as e:
+        lib.comm_create([])
+    assert e.value.status == lib.ERR_INVALID_ARGUMENT and "1 to 8 GPUs" in e.value.message
+    with pytest.raises(lib.CuteB200Error) as e:
+        lib.comm_create(list(range(9)))
+    assert e.value.status == lib.ERR_INVALID_ARGUMENT
+    assert lib.load().cute_b200_comm_create(1, None, None) == lib.ERR_NULL_POINTER
+    lib.comm_destroy(None)  # destroying nothing is fine
+    junk = ctypes.create_string_buffer(512)
+    d = lib.gemm_desc(256, 128, 64, lib.BF16, lib.F32)
+    for call in (lambda: lib.comm_destroy(ctypes.addressof(junk)), lambda: lib.comm_info(ctypes.addressof(junk)),
+                 lambda: lib.gemm_tn_sharded(ctypes.addressof(junk), d, [1], [1], [1]),
+                 lambda: lib.gemm_tn_sharded_host(ctypes.addressof(junk), d, 1, 1, 1)):
+        with pytest.raises(lib.CuteB200Error) as e:
+            call()
+        assert e.value.status == lib.ERR_INVALID_ARGUMENT and "not a communicator" in e.value.message
+    import torch
+    if not torch.cuda.is_available():
+        with pytest.raises(lib.CuteB200Error) as e:
+            lib.comm_create([0])
+        assert e.value.status == lib.ERR_NO_DEVICE
+
+
 def test_argument_checks_come_before_the_device(lib):
     # check_launch runs before any CUDA call (src/cuda.rs:452), so its
     # messages can be compared without a GPU.

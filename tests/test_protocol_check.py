@@ -3,7 +3,7 @@ instantiates is clean, and each deliberate protocol bug is reported as the kind
 of error the reference's simulator reports for it (tests/diagnostics.rs)."""
 import pytest
 
-from cute_rs_b200.check import ProtocolError, check_gemm
+from cute_rs_b200.check import ProtocolError, check_gemm, tiling_from_library
 
 TILINGS = [dict(cta_group=g, stages=s, mh=mh, acc_bufs=ab) for g, s, mh, ab in
            [(2, 4, 2, 1), (1, 3, 2, 1), (2, 7, 1, 2), (1, 4, 1, 2), (2, 9, 1, 2), (2, 5, 2, 2), (1, 7, 1, 2)]]
@@ -13,6 +13,34 @@ TILINGS = [dict(cta_group=g, stages=s, mh=mh, acc_bufs=ab) for g, s, mh, ab in
 @pytest.mark.parametrize("units", [(1,), (8, 8, 8), (3, 5, 2, 7, 1), (13,) * 5, (4, 0, 4), (0, 0), (2, 2, 2, 2, 2, 2, 2)])
 def test_kernel_protocol_is_clean(tiling, units):
     check_gemm(units=units, **tiling)
+
+
+@pytest.mark.parametrize("units,chunks", [((8, 8, 8), 0), ((3, 5, 2, 7, 1), 0), ((13,) * 5, 0), ((4, 0, 4), 0), ((26, 1, 30), 0),
+                                          ((8, 8, 8), None), ((4, 0, 4), None)])
+def test_every_compiled_tiling_is_clean(lib, units, chunks):
+    """The schedule run with the ring depth, stage bytes, accumulator buffering,
+    barrier arrival counts and transaction bytes that the compiled kernel uses
+    (cute_b200_gemm_layout_info), for every tiling the library instantiates; with
+    chunks None the pusher runs too, with the kernel's chunks per tile."""
+    for g, tile_n, tile_m in lib.GEMM_TILINGS:
+        info = lib.gemm_layout_info(g, tile_n, tile_m)
+        push = info.push_chunks_per_tile if chunks is None else chunks
+        check_gemm(units=units, push_chunks=push, seeds=range(2), **tiling_from_library(info, g))
+
+
+def test_wrong_barrier_constants_would_be_seen(lib):
+    """What the tie to the library buys: were the kernel built with an arrival count
+    that forgets the second CTA of a pair, or with a transaction count of one CTA's
+    bytes, the schedule run with those constants fails."""
+    info = lib.gemm_layout_info(2, 256, 256)
+    good = tiling_from_library(info, 2)
+    check_gemm(units=(8, 8, 8), **good)
+    with pytest.raises(ProtocolError):
+        check_gemm(units=(8, 8, 8), **dict(good, tmem_empty_arrivals=info.tmem_empty_arrivals // 2))
+    with pytest.raises(ProtocolError):
+        check_gemm(units=(8, 8, 8), **dict(good, expect_tx=info.full_expect_tx_bytes // 2))
+    with pytest.raises(ProtocolError):
+        check_gemm(units=(8, 8, 8), **dict(good, tmem_empty_arrivals=info.tmem_empty_arrivals + 1))
 
 
 @pytest.mark.parametrize("mutation,kind", [
