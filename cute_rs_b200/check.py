@@ -174,6 +174,8 @@ class Machine:
 #   ("tma_load", cta, [C parts], buffer, bytes, barrier)   TMA reads the parts, writes the staging buffer
 #   ("tma_store", cta, buffer)               TMA reads the staging buffer (one bulk group per op)
 #   ("wait_read", keep)                      all but the newest `keep` bulk groups have read their source
+#   ("tma_store", cta, buffer, destination)  ... a store that also names what it writes (another GPU's rows of C)
+#   ("wait_all",)                            every bulk group of the thread is complete, its writes included
 def run(programs: dict, barriers: dict, seed: int = 0, tma_bytes_to=None, max_burst: int = 0, stalls=None) -> Machine:
     """Interleave the agents' programs: in every round each agent, in random order, runs until it
     blocks, or for a random number of steps up to `max_burst` when that is set (finer interleavings).
@@ -255,10 +257,15 @@ def run(programs: dict, barriers: dict, seed: int = 0, tma_bytes_to=None, max_bu
                     m.write(agent, buf, m.clock(a))
                     m.barriers[bar].complete_tx(m.clock(agent), nbytes)
                 elif kind == "tma_store":
-                    _, cta, buf = op
+                    cta, buf = op[1], op[2]
                     agent = f"tma_store{cta}.{pcs[a]}"
                     m.read(agent, buf, m.clock(a))
+                    if len(op) > 3:  # the destination in another GPU's memory, written by the same copy
+                        m.write(agent, op[3], m.clock(a))
                     m.groups.setdefault(a, []).append(m.clock(agent).copy())
+                elif kind == "wait_all":  # cp.async.bulk.wait_group 0: reads and writes of every group are complete
+                    for g in m.groups.get(a, []):
+                        m.clock(a).join(g)
                 elif kind == "wait_read":
                     groups = m.groups.get(a, [])
                     for g in groups[:len(groups) - op[1]]:
@@ -402,6 +409,52 @@ def gemm_schedule(cta_group: int = 2, stages: int = 4, mh: int = 2, acc_bufs: in
                 pushed += push_chunks
             it += 1
     return programs, barriers
+
+
+def signal_schedule(ctas: int = 4, chunks: int = 3, mutations=()):
+    """The end of a several-destination launch with completion counters, and the owner of one
+    destination waiting for it (cute_b200_gemm_tn_multi_signal / cute_b200_wait_signal).
+
+    Every CTA's pusher thread stores its chunks into the peer's rows of C (bulk stores from a
+    staging buffer it has filled), waits for all its bulk groups, and passes the CTA's closing
+    barrier; the CTA's first thread then counts the CTA in on the device's counter; whoever
+    brings that counter to the number of CTAs adds 1 to the counter in the peer's memory; the
+    peer's waiting kernel polls that counter and then reads the rows.  Mutations:
+      "signal_without_store_wait"   the pusher does not wait for its bulk stores before the barrier
+      "signal_before_all_ctas"      the remote counter is raised when one CTA is still missing
+      "peer_reads_without_waiting"  the owner reads its rows without polling the counter
+      "peer_expects_another_sender" the owner waits for one count more than anybody sends
+    """
+    mut = set(mutations)
+    programs, barriers = {}, {}
+    for c in range(ctas):
+        p = programs[f"pusher{c}"] = []
+        for ch in range(chunks):
+            p.append(("st", f"staging{c}.{ch}"))                     # stands for the TMA load that fills the buffer
+            p.append(("tma_store", c, f"staging{c}.{ch}", f"peer_c.{c}.{ch}"))
+        if "signal_without_store_wait" not in mut:
+            p.append(("wait_all",))
+        p.append(("signal", f"cta_barrier{c}"))                      # the closing __syncthreads of the CTA
+        t = programs[f"thread0.{c}"] = []
+        t.append(("wait_count", f"cta_barrier{c}", 1))
+        t.append(("signal", "device_done"))
+    last = programs["last_cta"] = []                                 # the thread that sees the count complete
+    last.append(("wait_count", "device_done", ctas - (1 if "signal_before_all_ctas" in mut else 0)))
+    last.append(("signal", "peer_counter"))
+    owner = programs["owner"] = []
+    if "peer_reads_without_waiting" not in mut:
+        owner.append(("wait_count", "peer_counter", 2 if "peer_expects_another_sender" in mut else 1))
+    for c in range(ctas):
+        for ch in range(chunks):
+            owner.append(("ld", f"peer_c.{c}.{ch}"))
+    return programs, barriers
+
+
+def check_signal(seeds=range(6), **kw) -> None:
+    programs, barriers = signal_schedule(**kw)
+    for seed in seeds:
+        run(programs, barriers, seed=seed)
+        run(programs, barriers, seed=seed, max_burst=2)
 
 
 def tiling_from_library(info, cta_group: int) -> dict:

@@ -75,6 +75,9 @@ enum : uint32_t {
     WHERE_SIGNAL = 7  // cute_b200_wait_signal: the counter did not reach the expected value in time
 };
 
+#ifndef CB_FAST_DRAIN
+#define CB_FAST_DRAIN 1  // 0 builds the epilogue without the read-everything-then-store path (measurements)
+#endif
 #ifndef EPI_GROUPS_BIG
 #define EPI_GROUPS_BIG 2  // measured: four groups (16 warps) are no faster than two on 8192^3 (0.699 vs 0.695 ms)
 #endif
@@ -138,6 +141,7 @@ struct GemmParams {
     int c_vec_ok;  // C base and row pitch allow 16-byte (1) or 32-byte (2) accesses
     int debug;     // measurements and tests only: bit 0 skips the TMA loads, bit 1 the stores, bit 2 makes the
                    // producer issue nothing at all (every consumer wait then runs out), bit 3 shortens the limit
+    int k_rotate;            // every tile walks its k blocks from a start of its own (wrapping round), see the producer
     int splits;              // k is cut into this many ranges, one work unit each (1 = no split)
     size_t split_stride;     // bytes between the partial-sum planes of consecutive ranges
     uint32_t *status;
@@ -385,7 +389,15 @@ __global__ void __launch_bounds__(num_threads(BN, MH), 1)
                 const TileCoord tc = tile_coord(u.tile, p);
                 const int row_a = (tc.tm * CTA_GROUP + int(rank)) * C::A_ROWS;
                 const int row_b = tc.tn * BN + int(rank) * C::B_ROWS;
-                for (int kb = u.kb0; kb < u.kb1; kb++) {
+                // With a single column of tiles every row of A is read by one CTA only and all CTAs
+                // would walk k in step: at any moment the whole GPU reads one 128-byte column stripe of
+                // A, addresses that differ only in the bits above the row pitch, and the stripe lands on
+                // few memory channels.  Starting every tile at a k block of its own spreads the reads
+                // over the row.  (The sum of a tile then starts in the middle of k and wraps round.)
+                const int nkb = u.kb1 - u.kb0;
+                const int rot = (p.k_rotate && nkb > 1) ? int(((uint32_t(u.tile) * 2654435761u) >> 12) % uint32_t(nkb)) : 0;
+                for (int i = 0; i < nkb; i++) {
+                    const int kb = u.kb0 + (i + rot >= nkb ? i + rot - nkb : i + rot);
                     if (!wait_bar(empty_bar(s), ph ^ 1u, abort_flag, p.status, WHERE_PRODUCER, uint32_t(s), wait_limit)) {
                         ok = false;
                         break;
@@ -549,6 +561,48 @@ __global__ void __launch_bounds__(num_threads(BN, MH), 1)
                     for (int d = 0; d < p.extra_count; d++)
                         store_chunk<C_BF16>(p, p.extra_c[d], row0 + (i / CH) * BM, col_base + col_of(i), v, true);
             };
+#if CB_FAST_DRAIN
+            // The single-buffered accumulator (two halves of 256 columns fill TMEM): the MMA issuer
+            // of the NEXT tile waits for each half to be handed back, so what counts is how soon
+            // after the tile's last MMA a half is out of TMEM.  For the common result (whole tile
+            // inside C, bf16, 32-byte aligned rows, plain epilogue, one destination written here)
+            // a warp reads all its chunks of a half into registers with back-to-back tcgen05.ld,
+            // hands the half back, and only then converts and stores.
+            if constexpr (C_BF16 && C::ACC_BUFS == 1 && CH == 4) {
+                const bool whole = (tc.tm * CTA_GROUP + int(rank) + 1) * C::A_ROWS <= p.M && (tc.tn + 1) * BN <= p.N;
+                if (have_acc && plain && whole && p.c_vec_ok == 2 && !(p.debug & 2) && (p.push || p.extra_count == 0)) {
+#pragma unroll 1
+                    for (int h = 0; h < HALVES; h++) {
+                        uint32_t v[CH][32];
+#pragma unroll
+                        for (int c = 0; c < CH; c++) ptx::tmem_ld_32x32(taddr0 + uint32_t(h * C::HALF_COLS + col_of(c)), v[c]);
+                        ptx::tmem_ld_wait_all();
+#pragma unroll
+                        for (int c = 0; c < CH; c++) ptx::pin(v[c]);
+                        ptx::tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) {
+                            if constexpr (CTA_GROUP == 1) ptx::mbar_arrive(tempty_bar(buf, h));
+                            else ptx::mbar_arrive_cluster(ptx::mapa(tempty_bar(buf, h), 0));
+                        }
+                        __nv_bfloat16 *crow = reinterpret_cast<__nv_bfloat16 *>(cbase) + size_t(row0 + h * BM) * p.ldc + col_base;
+#pragma unroll
+                        for (int c = 0; c < CH; c++) {
+                            uint32_t w[16];
+#pragma unroll
+                            for (int j = 0; j < 16; j++) {
+                                const __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(v[c][2 * j]), __uint_as_float(v[c][2 * j + 1]));
+                                w[j] = *reinterpret_cast<const uint32_t *>(&hh);
+                            }
+                            ptx::st_global_v8(crow + col_of(c), w[0], w[1], w[2], w[3], w[4], w[5], w[6], w[7]);
+                            ptx::st_global_v8(crow + col_of(c) + 16, w[8], w[9], w[10], w[11], w[12], w[13], w[14], w[15]);
+                        }
+                    }
+                    goto tile_stored;
+                }
+            }
+#endif
+            {
             // Two register buffers: the TMEM read of the next chunk is in flight
             // while the current one is converted and stored.
             uint32_t va[32], vb[32];
@@ -564,6 +618,10 @@ __global__ void __launch_bounds__(num_threads(BN, MH), 1)
                     finish(i + 1, vb);
                 }
             }
+            }
+#if CB_FAST_DRAIN
+        tile_stored:
+#endif
             if (p.push) {
                 // This warp's part of the tile is in C: make the stores visible to the TMA unit
                 // (async proxy) and publish the warp's tile count for the pusher.
@@ -947,6 +1005,15 @@ double choose_tiling(int m, int n, int k, int c_bytes, int sm_count, int want_gr
     return best;
 }
 
+// Whether the tiles of this problem start their k loops at offsets of their own: one column of
+// tiles, a B small enough to stay in L2, enough k blocks per unit for a start offset to matter.
+int want_k_rotate(const cute_b200_gemm_desc &d, int bn, int splits) {
+    int rotate = ((d.n + bn - 1) / bn == 1 && size_t(d.n) * d.k * 2 <= (size_t(32) << 20) && (d.k + BK - 1) / BK / splits >= 8) ? 1 : 0;
+    if (d.tuning[0] & 32) rotate = 0;
+    if (d.tuning[0] & 64) rotate = 1;
+    return rotate;
+}
+
 // Grow-only scratch of the split-k path, one per device, shared by every
 // stream.  `idle` is recorded behind the second pass of each split GEMM and the
 // next split GEMM's stream waits for it before its first pass, so two calls on
@@ -1093,6 +1160,7 @@ cute_b200_status gemm_tn_static(const cute_b200_gemm_desc &d, uint64_t a, uint64
     p.status = shared_status ? shared_status : setup->status;
     p.debug = d.tuning[0] & (4 | 8);  // the two test knobs of the bounded waits; the measurement knobs stay off
     p.group_m = d.tuning[1];
+    p.k_rotate = want_k_rotate(d, bn, splits);
     p.splits = splits;
     p.split_stride = plane * 4;
     p.c_vec_ok = (size_t(d.n) * 4) % 32 == 0 ? 2 : ((size_t(d.n) * 4) % 16 == 0 ? 1 : 0);
@@ -1262,6 +1330,7 @@ static cute_b200_status gemm_tn_ex(const cute_b200_gemm_desc &d, uint64_t a, uin
     p.group_m = d.tuning[1];
     p.splits = splits;
     p.split_stride = 0;
+    p.k_rotate = want_k_rotate(d, bn, splits);
     p.extra_count = ex.extra_count;
     for (int i = 0; i < ex.extra_count; i++) p.extra_c[i] = reinterpret_cast<void *>(ex.extra_c[i]);
     if (ex.signal && ex.extra_count > 0) {

@@ -135,6 +135,19 @@ class PeerBuffer:
         self.ptrs = [self.local if r == rank else _lib.ipc_open(handles[r]) for r in range(world)]
         dist.barrier(group=group)
 
+    def reset_signals(self, group=None) -> None:
+        """Zero every rank's completion counters and start counting steps again (after a step in
+        which a rank did not send, which leaves its counters one short everywhere).  Collective."""
+        import torch
+        import torch.distributed as dist
+        torch.cuda.synchronize()
+        dist.barrier(group=group)
+        zeros = torch.zeros(self.FLAG_BYTES, dtype=torch.uint8, device="cuda")
+        _lib.copy_async(self.local + self.flag_offset, zeros.data_ptr(), self.FLAG_BYTES, torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        self.steps = 0
+        dist.barrier(group=group)
+
     def tensor(self, shape, dtype):
         import torch
 

@@ -102,7 +102,9 @@ typedef struct {
     int32_t tuning[2]; /* zero.  Measurement and test knobs: [0] bit 0 skips the loads, bit 1 the stores (results
                           are then meaningless), bits 2+3 make every in-kernel wait run out after 20 ms so that
                           the bounded-wait report can be tested, bit 4 makes cute_b200_gemm_tn_multi store to its
-                          destinations from registers instead of by TMA; [1] row tiles walked per column step */
+                          destinations from registers instead of by TMA, bit 5 switches off (bit 6 forces) the
+                          per-tile start offset of the k loop that single-column problems get;
+                          [1] row tiles walked per column step */
 } cute_b200_gemm_desc;
 
 cute_b200_status cute_b200_gemm_tn(const cute_b200_gemm_desc *desc, uint64_t dA, uint64_t dB, uint64_t dC,

@@ -3,7 +3,7 @@ instantiates is clean, and each deliberate protocol bug is reported as the kind
 of error the reference's simulator reports for it (tests/diagnostics.rs)."""
 import pytest
 
-from cute_rs_b200.check import ProtocolError, check_gemm, tiling_from_library
+from cute_rs_b200.check import ProtocolError, check_gemm, check_signal, tiling_from_library
 
 TILINGS = [dict(cta_group=g, stages=s, mh=mh, acc_bufs=ab) for g, s, mh, ab in
            [(2, 4, 2, 1), (1, 3, 2, 1), (2, 7, 1, 2), (1, 4, 1, 2), (2, 9, 1, 2), (2, 5, 2, 2), (1, 7, 1, 2)]]
@@ -104,3 +104,22 @@ def test_one_shared_tile_count_is_a_race_when_a_warp_falls_behind():
     with pytest.raises(ProtocolError) as e:
         held_back(("shared_tile_counter",))
     assert e.value.kind in ("uninitialised", "race")
+
+
+# ---- completion counters of the several-destination form ----------------------------------
+@pytest.mark.parametrize("ctas,chunks", [(1, 1), (4, 3), (8, 2)])
+def test_completion_signal_protocol_is_clean(ctas, chunks):
+    check_signal(ctas=ctas, chunks=chunks)
+
+
+@pytest.mark.parametrize("mutation,kind", [
+    ("signal_without_store_wait", ("race", "uninitialised")),   # the owner reads rows whose bulk store may not have landed
+    ("signal_before_all_ctas", ("race", "uninitialised")),      # ... rows of the CTA that was not waited for
+    ("peer_reads_without_waiting", ("race", "uninitialised")),
+    ("peer_expects_another_sender", "deadlock"),                # what the bounded wait turns into a reported timeout
+])
+def test_completion_signal_bugs_are_reported(mutation, kind):
+    kinds = (kind,) if isinstance(kind, str) else kind
+    with pytest.raises(ProtocolError) as e:
+        check_signal(ctas=4, chunks=3, mutations=(mutation,), seeds=range(12))
+    assert e.value.kind in kinds, str(e.value)
