@@ -231,9 +231,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--skip-extras", action="store_true", help="skip cpu_baseline / e2e / secondary kernels (profiling runs)")
-    ap.add_argument("--only", choices=["add", "sgemm", "multi"],
+    ap.add_argument("--only", choices=["add", "sgemm", "multi", "gemm"],
                     help="run just this secondary kernel (for ncu captures) and exit; multi = the several-destination GEMM "
-                         "with its copies of C on this one GPU")
+                         "with its copies of C on this one GPU; gemm = runtime_gemm bf16 -> bf16 of --shape")
+    ap.add_argument("--shape", default="8192,128,8192", help="--only gemm: m,n,k")
+    ap.add_argument("--tiling", default="0,0,0,0", help="--only gemm: cta_group,tile_n,tile_m,split_k (0 = the library chooses)")
     ap.add_argument("--log2n", type=int, default=28, help="--only add: log2 of the element count")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
@@ -261,6 +263,9 @@ def main():
             res = bench_add(lib, torch, peaks(), 1 << args.log2n)
         elif args.only == "sgemm":
             res = bench_sgemm(lib, torch)
+        elif args.only == "gemm":
+            res = bench_gemm_shape(lib, torch, [int(x) for x in args.shape.split(",")], [int(x) for x in args.tiling.split(",")],
+                                   max(args.steps, 1) if args.steps != 100 else 20, peaks())
         else:
             res = bench_multi(lib, torch)
         print(json.dumps(res))
@@ -682,6 +687,46 @@ def bench_sgemm(lib, torch):
     ms = e0.elapsed_time(e1) / 10
     return {"workload": "sgemm_nt f32 4096^3 column-major, alpha 1.5, beta 0.5", "tflops": 2.0 * n ** 3 / ms / 1e9, "ms": ms,
             "bound": "fp32 FFMA pipe", "peak_nominal": 148 * 128 * 2 * 1.965e9 / 1e12}
+
+
+def bench_gemm_shape(lib, torch, shape, tiling, iters, pk):
+    """One runtime_gemm shape (bf16 in, bf16 out, normal(0, 0.02) seed 3), timed with CUDA events, with
+    torch.matmul on the same operands beside it and the two rooflines of the shape: the tensor pipe
+    (2mnk at the measured bf16 rate) and HBM (the operands and the result once, at the measured copy rate)."""
+    m, n, k = shape
+    g = torch.Generator(device="cuda").manual_seed(3)
+    A = (torch.randn(m, k, device="cuda", generator=g) * 0.02).bfloat16()
+    B = (torch.randn(n, k, device="cuda", generator=g) * 0.02).bfloat16()
+    C = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+    d = lib.gemm_desc(m, n, k, lib.BF16, lib.BF16, cta_group=tiling[0], tile_n=tiling[1], tile_m=tiling[2], split_k=tiling[3])
+    s = torch.cuda.current_stream().cuda_stream
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+
+    n0 = lib.launch_count()
+    ms = timed(lambda: lib.gemm_tn(d, A.data_ptr(), B.data_ptr(), C.data_ptr(), s))
+    launches = (lib.launch_count() - n0) // (iters + 3)
+    Bt = B.t()
+    ms_t = timed(lambda: torch.matmul(A, Bt))
+    flop, byts = 2.0 * m * n * k, 2.0 * (m * k + n * k + m * n)
+    t_tensor, t_hbm = flop / (pk["bf16_tflops"] * 1e12) * 1e3, byts / (pk["hbm_gbs"] * 1e9) * 1e3
+    chk = BandCheck(to_bits(torch, A), to_bits(torch, B), three_bands(m), k)
+    got, off = band_bits(torch, C, chk.bands)
+    return {"workload": f"runtime_gemm bf16 {m}x{n}x{k} -> bf16, normal(0,0.02) seed 3", "ms": ms, "tflops": flop / ms / 1e9,
+            "kernels_per_call": launches, "torch_matmul_ms": ms_t, "ratio_to_torch": ms / ms_t,
+            "bound": "hbm" if t_hbm > t_tensor else "tensor", "roofline_ms": max(t_tensor, t_hbm),
+            "frac_of_roofline": max(t_tensor, t_hbm) / ms, "algorithmic_bytes": byts, "gbs": byts / ms / 1e6,
+            "parity": chk.check(got, off), "status": list(lib.device_status())}
 
 
 def bench_multi(lib, torch, copies=3):

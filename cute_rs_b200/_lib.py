@@ -47,10 +47,10 @@ class GemmDesc(ctypes.Structure):
 class GemmLayout(ctypes.Structure):
     """cute_b200_gemm_layout: the constants one GEMM tiling is compiled from."""
     _fields_ = [(name, ctypes.c_uint32) for name in (
-        "instruction_descriptor", "umma_m", "umma_n", "umma_k", "block_k", "cta_rows", "a_stage_bytes", "b_stage_bytes",
-        "stage_bytes", "stages", "accumulator_halves", "half_columns", "accumulator_buffers", "tmem_columns", "threads",
+        "instruction_descriptor", "umma_m", "umma_n", "umma_k", "block_k", "cta_rows", "a_block_bytes", "b_block_bytes",
+        "k_blocks_per_stage", "stage_bytes", "stages", "accumulator_halves", "half_columns", "accumulator_buffers", "tmem_columns", "threads",
         "epilogue_warps", "full_arrivals", "empty_arrivals", "tmem_full_arrivals", "tmem_empty_arrivals",
-        "full_expect_tx_bytes", "push_chunk_bytes", "push_chunk_rows", "push_chunks_per_tile", "shared_memory_bytes",
+        "full_expect_tx_bytes_per_k_block", "push_chunk_bytes", "push_chunk_rows", "push_chunks_per_tile", "shared_memory_bytes",
         "descriptor_k_step")] + [("smem_descriptor", ctypes.c_uint64)]
 
 

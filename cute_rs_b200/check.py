@@ -288,11 +288,14 @@ def run(programs: dict, barriers: dict, seed: int = 0, tma_bytes_to=None, max_bu
 # ---- the GEMM kernel's protocol ------------------------------------------------------
 def gemm_schedule(cta_group: int = 2, stages: int = 4, mh: int = 2, acc_bufs: int = 1, units=(8, 8, 8),
                   stage_bytes: int = 48 * 1024, mutations=(), push_chunks: int = 0, epilogue_warps: int = 8,
-                  tmem_empty_arrivals: int = None, expect_tx: int = None, push_bytes: int = 16 * 1024):
+                  tmem_empty_arrivals: int = None, expect_tx: int = None, push_bytes: int = 16 * 1024, kps: int = 1):
     """Programs and barriers of gemm_tn_kernel for one cluster.
 
     `units` lists the k-block count of each work unit the cluster processes (0 =
-    an empty k range).  `tmem_empty_arrivals` (count the accumulator-free barriers
+    an empty k range).  `kps` k blocks share one ring stage (one full/empty
+    barrier pair; the last stage of a unit may hold fewer); `stage_bytes` are the
+    bytes of ONE k block in one CTA, `expect_tx` what the leader announces per k
+    block.  `tmem_empty_arrivals` (count the accumulator-free barriers
     are initialised with) and `expect_tx` (bytes the leader announces per stage)
     default to what the schedule itself implies - one arrival per epilogue warp of
     the group, every CTA's stage bytes; `tiling_from_library` passes the values the
@@ -343,23 +346,25 @@ def gemm_schedule(cta_group: int = 2, stages: int = 4, mh: int = 2, acc_bufs: in
     it = 0     # non-empty units so far
     for kbs in units:
         buf, use = it % acc_bufs, it // acc_bufs
-        for kb in range(kbs):
+        for kb0 in range(0, kbs, kps):
+            nk = min(kps, kbs - kb0)
             s, rnd = fill % stages, fill // stages
             for c in ctas:
                 p = programs[f"producer{c}"]
                 if "producer_skips_empty_wait" not in mut:
                     p.append(("wait", f"empty{c}.{s}", rnd - 1 + (1 if "wrong_empty_parity" in mut else 0)))
                 if c == 0:
-                    total = stage_bytes if "expect_tx_short" in mut else (expect_tx if expect_tx is not None else stage_bytes * cta_group)
-                    p.append(("expect", f"full.{s}", total))
-                p.append(("tma", c, s, stage_bytes, f"full.{s}"))
+                    per_kb = stage_bytes if "expect_tx_short" in mut else (expect_tx if expect_tx is not None else stage_bytes * cta_group)
+                    p.append(("expect", f"full.{s}", nk * per_kb))
+                p.append(("tma", c, s, nk * stage_bytes, f"full.{s}"))
             mma = programs["mma"]
             if "mma_skips_full_wait" not in mut:
                 mma.append(("wait", f"full.{s}", rnd))
-            for h in range(mh):
-                if kb == 0 and "mma_skips_tmem_wait" not in mut:
-                    mma.append(("wait", f"tempty.{buf}.{h}", use - 1))
-                mma.append(("mma", [f"smem{c}.{s}" for c in ctas], [f"tmem{c}.{buf}.{h}" for c in ctas], kb == 0))
+            for kb in range(kb0, kb0 + nk):
+                for h in range(mh):
+                    if kb == 0 and "mma_skips_tmem_wait" not in mut:
+                        mma.append(("wait", f"tempty.{buf}.{h}", use - 1))
+                    mma.append(("mma", [f"smem{c}.{s}" for c in ctas], [f"tmem{c}.{buf}.{h}" for c in ctas], kb == 0))
             for c in ctas:
                 if c == 0 or "no_peer_commit" not in mut:
                     mma.append(("commit", f"empty{c}.{s}"))
@@ -463,10 +468,11 @@ def tiling_from_library(info, cta_group: int) -> dict:
     accumulator halves and buffers, epilogue warps, barrier counts, pusher chunk)."""
     assert (info.full_arrivals, info.empty_arrivals, info.tmem_full_arrivals) == (1, 1, 1), \
         "the schedule models one producer arrival, one commit per stage and one per accumulator"
+    assert info.stage_bytes == info.k_blocks_per_stage * (info.a_block_bytes + info.b_block_bytes)
     return dict(cta_group=cta_group, stages=info.stages, mh=info.accumulator_halves, acc_bufs=info.accumulator_buffers,
-                stage_bytes=info.stage_bytes, epilogue_warps=info.epilogue_warps,
-                tmem_empty_arrivals=info.tmem_empty_arrivals, expect_tx=info.full_expect_tx_bytes,
-                push_bytes=info.push_chunk_bytes)
+                stage_bytes=info.a_block_bytes + info.b_block_bytes, kps=info.k_blocks_per_stage,
+                epilogue_warps=info.epilogue_warps, tmem_empty_arrivals=info.tmem_empty_arrivals,
+                expect_tx=info.full_expect_tx_bytes_per_k_block, push_bytes=info.push_chunk_bytes)
 
 
 def check_gemm(seeds=range(4), **kw) -> None:

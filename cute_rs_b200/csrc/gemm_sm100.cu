@@ -107,7 +107,14 @@ struct Cfg {
     static constexpr int UMMA_M = (HALF ? 64 : BM) * CTA_GROUP;   // rows of one MMA over the whole group
     static constexpr uint32_t A_BYTES = A_ROWS * BK * 2;
     static constexpr uint32_t B_BYTES = B_ROWS * BK * 2;
-    static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr uint32_t KB_BYTES = A_BYTES + B_BYTES;  // one k block (64 of k) of both operands
+    // k blocks per ring stage.  The thread that issues the MMAs pays a fixed price per stage (a wait on
+    // the stage's barrier, a fence, the commits that free it: about 175 clocks during which the tensor
+    // core runs dry, measured with one thread issuing M 128 x N 128 MMAs), so a stage has to hold
+    // enough MMA time to make that small: tiles whose k block is short on math (128 columns, or 64
+    // rows) put several k blocks behind one barrier.  The ring holds the same bytes either way.
+    static constexpr int KPS = HALF ? (BN == 128 ? 4 : 2) : ((MH == 1 && BN == 128) ? 2 : 1);
+    static constexpr uint32_t STAGE_BYTES = KPS * KB_BYTES;
     static constexpr int STAGES = (RING_BYTES / STAGE_BYTES) > MAX_STAGES ? MAX_STAGES : int(RING_BYTES / STAGE_BYTES);
     static constexpr int HALF_COLS = HALF ? BN / 2 : BN;             // TMEM columns of one 128-lane accumulator
     static constexpr int ACC_COLS = HALVES * HALF_COLS;              // TMEM columns of one accumulator set
@@ -118,7 +125,7 @@ struct Cfg {
     // frees it and one publishes an accumulator, every epilogue warp of the group hands a half back.
     static constexpr uint32_t FULL_ARRIVALS = 1, EMPTY_ARRIVALS = 1, TFULL_ARRIVALS = 1;
     static constexpr uint32_t TEMPTY_ARRIVALS = 4 * epilogue_groups(BN, MH) * CTA_GROUP;
-    static constexpr uint32_t EXPECT_TX = CTA_GROUP * STAGE_BYTES;  // bytes the (leader's) full barrier counts per stage
+    static constexpr uint32_t EXPECT_TX_PER_KB = CTA_GROUP * KB_BYTES;  // bytes the (leader's) full barrier counts per k block of a stage
     static_assert(STAGES >= 2 && STAGES <= MAX_STAGES, "ring depth");
     static_assert(ACC_COLS * ACC_BUFS <= 512, "accumulators exceed TMEM");
     static_assert(SMEM_BYTES <= 227 * 1024, "shared memory");
@@ -141,7 +148,6 @@ struct GemmParams {
     int c_vec_ok;  // C base and row pitch allow 16-byte (1) or 32-byte (2) accesses
     int debug;     // measurements and tests only: bit 0 skips the TMA loads, bit 1 the stores, bit 2 makes the
                    // producer issue nothing at all (every consumer wait then runs out), bit 3 shortens the limit
-    int k_rotate;            // every tile walks its k blocks from a start of its own (wrapping round), see the producer
     int splits;              // k is cut into this many ranges, one work unit each (1 = no split)
     size_t split_stride;     // bytes between the partial-sum planes of consecutive ranges
     uint32_t *status;
@@ -389,34 +395,36 @@ __global__ void __launch_bounds__(num_threads(BN, MH), 1)
                 const TileCoord tc = tile_coord(u.tile, p);
                 const int row_a = (tc.tm * CTA_GROUP + int(rank)) * C::A_ROWS;
                 const int row_b = tc.tn * BN + int(rank) * C::B_ROWS;
-                // With a single column of tiles every row of A is read by one CTA only and all CTAs
-                // would walk k in step: at any moment the whole GPU reads one 128-byte column stripe of
-                // A, addresses that differ only in the bits above the row pitch, and the stripe lands on
-                // few memory channels.  Starting every tile at a k block of its own spreads the reads
-                // over the row.  (The sum of a tile then starts in the middle of k and wraps round.)
                 const int nkb = u.kb1 - u.kb0;
-                const int rot = (p.k_rotate && nkb > 1) ? int(((uint32_t(u.tile) * 2654435761u) >> 12) % uint32_t(nkb)) : 0;
-                for (int i = 0; i < nkb; i++) {
-                    const int kb = u.kb0 + (i + rot >= nkb ? i + rot - nkb : i + rot);
+                for (int i0 = 0; i0 < nkb; i0 += C::KPS) {
+                    const int nk = nkb - i0 < C::KPS ? nkb - i0 : C::KPS;  // k blocks of this stage (the last may be short)
                     if (!wait_bar(empty_bar(s), ph ^ 1u, abort_flag, p.status, WHERE_PRODUCER, uint32_t(s), wait_limit)) {
                         ok = false;
                         break;
                     }
-                    const uint32_t a_dst = ring + uint32_t(s) * C::STAGE_BYTES;
-                    const uint32_t b_dst = a_dst + C::A_BYTES;
+                    const uint32_t dst0 = ring + uint32_t(s) * C::STAGE_BYTES;
+                    const int k0 = (u.kb0 + i0) * BK;
                     if (p.debug & 1) {
                         if (rank == 0) ptx::mbar_arrive(full_bar(s));
                     } else if constexpr (CTA_GROUP == 1) {
-                        ptx::mbar_arrive_expect_tx(full_bar(s), C::EXPECT_TX);
-                        ptx::tma_load_2d(a_dst, &tmA, full_bar(s), kb * BK, row_a);
-                        ptx::tma_load_2d(b_dst, &tmB, full_bar(s), kb * BK, row_b);
+                        ptx::mbar_arrive_expect_tx(full_bar(s), uint32_t(nk) * C::EXPECT_TX_PER_KB);
+#pragma unroll
+                        for (int kk = 0; kk < C::KPS; kk++)
+                            if (kk < nk) {
+                                ptx::tma_load_2d(dst0 + uint32_t(kk) * C::KB_BYTES, &tmA, full_bar(s), k0 + kk * BK, row_a);
+                                ptx::tma_load_2d(dst0 + uint32_t(kk) * C::KB_BYTES + C::A_BYTES, &tmB, full_bar(s), k0 + kk * BK, row_b);
+                            }
                     } else {
                         // Both CTAs' bytes are counted on the leader's barrier,
                         // which is the one the MMA issuer waits on.
-                        if (rank == 0) ptx::mbar_arrive_expect_tx(full_bar(s), C::EXPECT_TX);
+                        if (rank == 0) ptx::mbar_arrive_expect_tx(full_bar(s), uint32_t(nk) * C::EXPECT_TX_PER_KB);
                         const uint32_t leader_full = ptx::mapa(full_bar(s), 0);
-                        ptx::tma_load_2d_pair(a_dst, &tmA, leader_full, kb * BK, row_a);
-                        ptx::tma_load_2d_pair(b_dst, &tmB, leader_full, kb * BK, row_b);
+#pragma unroll
+                        for (int kk = 0; kk < C::KPS; kk++)
+                            if (kk < nk) {
+                                ptx::tma_load_2d_pair(dst0 + uint32_t(kk) * C::KB_BYTES, &tmA, leader_full, k0 + kk * BK, row_a);
+                                ptx::tma_load_2d_pair(dst0 + uint32_t(kk) * C::KB_BYTES + C::A_BYTES, &tmB, leader_full, k0 + kk * BK, row_b);
+                            }
                     }
                     filled |= 1u << s;
                     filled_parity = (filled_parity & ~(1u << s)) | (ph << s);
@@ -452,33 +460,42 @@ __global__ void __launch_bounds__(num_threads(BN, MH), 1)
                 const uint32_t aph = uint32_t(it / C::ACC_BUFS) & 1u;
                 it++;
                 const uint32_t d_tmem = tmem_base + uint32_t(buf * C::ACC_COLS);
-                for (int kb = u.kb0; kb < u.kb1 && ok; kb++) {
+                const int nkb = u.kb1 - u.kb0;
+                for (int i0 = 0; i0 < nkb && ok; i0 += C::KPS) {
+                    const int nk = nkb - i0 < C::KPS ? nkb - i0 : C::KPS;
                     if (!wait_bar(full_bar(s), ph, abort_flag, p.status, WHERE_MMA_FULL, uint32_t(s), wait_limit)) {
                         ok = false;
                         break;
                     }
                     ptx::tc_fence_after();
-                    const uint32_t a_src = ring + uint32_t(s) * C::STAGE_BYTES;
-                    const uint64_t b_desc = sw128_desc(a_src + C::A_BYTES);
+                    const uint32_t stage = ring + uint32_t(s) * C::STAGE_BYTES;
 #pragma unroll
-                    for (int h = 0; h < HALVES; h++) {
-                        if (kb == u.kb0) {
-                            // The epilogue must have drained this half of the buffer
-                            // (a fresh barrier passes at once).
-                            if (!wait_bar(tempty_bar(buf, h), aph ^ 1u, abort_flag, p.status, WHERE_MMA_TMEM,
-                                          uint32_t(buf * 2 + h), wait_limit)) {
-                                ok = false;
-                                break;
+                    for (int kk = 0; kk < C::KPS; kk++) {
+                        if (kk >= nk) break;
+                        const bool first = (i0 == 0 && kk == 0);  // the unit's first k block overwrites the accumulator
+                        const uint32_t a_src = stage + uint32_t(kk) * C::KB_BYTES;
+                        const uint64_t b_desc = sw128_desc(a_src + C::A_BYTES);
+#pragma unroll
+                        for (int h = 0; h < HALVES; h++) {
+                            if (first) {
+                                // The epilogue must have drained this half of the buffer
+                                // (a fresh barrier passes at once).
+                                if (!wait_bar(tempty_bar(buf, h), aph ^ 1u, abort_flag, p.status, WHERE_MMA_TMEM,
+                                              uint32_t(buf * 2 + h), wait_limit)) {
+                                    ok = false;
+                                    break;
+                                }
+                                ptx::tc_fence_after();
                             }
-                            ptx::tc_fence_after();
-                        }
-                        const uint64_t a_desc = sw128_desc(a_src + uint32_t(h) * (BM * BK * 2));
+                            const uint64_t a_desc = sw128_desc(a_src + uint32_t(h) * (BM * BK * 2));
 #pragma unroll
-                        for (int j = 0; j < BK / UMMA_K; j++) {
-                            ptx::umma_f16<CTA_GROUP>(d_tmem + uint32_t(h * C::HALF_COLS), a_desc + DESC_K_STEP * j, b_desc + DESC_K_STEP * j, p.idesc,
-                                                     (kb > u.kb0 || j > 0) ? 1u : 0u);
+                            for (int j = 0; j < BK / UMMA_K; j++) {
+                                ptx::umma_f16<CTA_GROUP>(d_tmem + uint32_t(h * C::HALF_COLS), a_desc + DESC_K_STEP * j, b_desc + DESC_K_STEP * j,
+                                                         p.idesc, (!first || j > 0) ? 1u : 0u);
+                            }
+                            issued = true;
                         }
-                        issued = true;
+                        if (!ok) break;
                     }
                     if (!ok) break;
                     ptx::umma_commit<CTA_GROUP>(empty_bar(s));
@@ -934,11 +951,14 @@ cute_b200_status set_smem_limit() {
 // pair tile is the reference point); used only to rank candidates.  mh counts the
 // 128-row accumulators per CTA, 0 = the 64-row pair tile.
 double tiling_efficiency(int group, int bn, int mh) {
-    if (mh == 0) return bn == 128 ? 0.55 : 0.70;
+    // The 64-row pair tile is bound by the rate at which one thread can issue cta_group::2 MMAs
+    // (about 115 clocks each, whatever their size): 8192 x 128 x 8192 runs 0.23 us per k block,
+    // 8192 x 256 x 8192 0.31 us.
+    if (mh == 0) return bn == 128 ? 0.45 : 0.67;
     double e = 1.0;
     if (group == 1) e *= (mh == 2 ? 0.96 : 0.86);
     else if (mh == 1) e *= 0.92;
-    if (bn == 128) e *= (mh == 2 ? 0.85 : 0.72);
+    if (bn == 128) e *= (mh == 2 ? 0.85 : (group == 1 ? 0.82 : 0.72));
     return e;
 }
 
@@ -963,7 +983,7 @@ double choose_tiling(int m, int n, int k, int c_bytes, int sm_count, int want_gr
     // cluster barrier around the TMEM set-up); measured on one-wave problems: 1024^3 12.7 / 10.6 us,
     // 2048^3 20.7 / 18.6, 3072^3 41.2 / 39.6 (pair / single), equal from 4096^3 on.
     const double pair_start = 2.0e-6;
-    const double hbm = 5.0e12;
+    const double hbm = 4.5e12;  // what rows of A read as 128-byte pieces, 16 KiB apart, reach (cuBLAS: 4.7e12 on the same shape)
     const int k_blocks = (k + BK - 1) / BK;
     if (max_splits > 16) max_splits = 16;
     if (max_splits > k_blocks) max_splits = k_blocks;
@@ -996,22 +1016,13 @@ double choose_tiling(int m, int n, int k, int c_bytes, int sm_count, int want_gr
                     if (stream_time > unit_time) unit_time = stream_time;
                     double t = waves * (unit_time + unit_latency);
                     if (g == 2) t += pair_start;
-                    if (s > 1) t += (double(s + 1) * m * n * 4 + double(m) * n * c_bytes) / hbm + 3e-6;
+                    if (s > 1) t += (double(s + 1) * m * n * 4 + double(m) * n * c_bytes) / hbm + 6e-6;  // + the second launch
                     if (t < best) {
                         best = t;
                         *group = g, *bn = b, *mh = h, *splits = s;
                     }
                 }
     return best;
-}
-
-// Whether the tiles of this problem start their k loops at offsets of their own: one column of
-// tiles, a B small enough to stay in L2, enough k blocks per unit for a start offset to matter.
-int want_k_rotate(const cute_b200_gemm_desc &d, int bn, int splits) {
-    int rotate = ((d.n + bn - 1) / bn == 1 && size_t(d.n) * d.k * 2 <= (size_t(32) << 20) && (d.k + BK - 1) / BK / splits >= 8) ? 1 : 0;
-    if (d.tuning[0] & 32) rotate = 0;
-    if (d.tuning[0] & 64) rotate = 1;
-    return rotate;
 }
 
 // Grow-only scratch of the split-k path, one per device, shared by every
@@ -1160,7 +1171,6 @@ cute_b200_status gemm_tn_static(const cute_b200_gemm_desc &d, uint64_t a, uint64
     p.status = shared_status ? shared_status : setup->status;
     p.debug = d.tuning[0] & (4 | 8);  // the two test knobs of the bounded waits; the measurement knobs stay off
     p.group_m = d.tuning[1];
-    p.k_rotate = want_k_rotate(d, bn, splits);
     p.splits = splits;
     p.split_stride = plane * 4;
     p.c_vec_ok = (size_t(d.n) * 4) % 32 == 0 ? 2 : ((size_t(d.n) * 4) % 16 == 0 ? 1 : 0);
@@ -1330,7 +1340,6 @@ static cute_b200_status gemm_tn_ex(const cute_b200_gemm_desc &d, uint64_t a, uin
     p.group_m = d.tuning[1];
     p.splits = splits;
     p.split_stride = 0;
-    p.k_rotate = want_k_rotate(d, bn, splits);
     p.extra_count = ex.extra_count;
     for (int i = 0; i < ex.extra_count; i++) p.extra_c[i] = reinterpret_cast<void *>(ex.extra_c[i]);
     if (ex.signal && ex.extra_count > 0) {
@@ -1403,13 +1412,14 @@ static void fill_layout(bool ab_bf16, bool c_bf16, uint32_t smem_addr, cute_b200
     o->umma_m = C::UMMA_M, o->umma_n = BN, o->umma_k = UMMA_K;
     o->block_k = BK;
     o->cta_rows = C::A_ROWS;
-    o->a_stage_bytes = C::A_BYTES, o->b_stage_bytes = C::B_BYTES, o->stage_bytes = C::STAGE_BYTES, o->stages = C::STAGES;
+    o->a_block_bytes = C::A_BYTES, o->b_block_bytes = C::B_BYTES, o->k_blocks_per_stage = C::KPS;
+    o->stage_bytes = C::STAGE_BYTES, o->stages = C::STAGES;
     o->accumulator_halves = C::HALVES, o->half_columns = C::HALF_COLS, o->accumulator_buffers = C::ACC_BUFS;
     o->tmem_columns = C::TMEM_COLS;
     o->threads = num_threads(BN, MH), o->epilogue_warps = 4 * epilogue_groups(BN, MH);
     o->full_arrivals = C::FULL_ARRIVALS, o->empty_arrivals = C::EMPTY_ARRIVALS, o->tmem_full_arrivals = C::TFULL_ARRIVALS;
     o->tmem_empty_arrivals = C::TEMPTY_ARRIVALS;
-    o->full_expect_tx_bytes = C::EXPECT_TX;
+    o->full_expect_tx_bytes_per_k_block = C::EXPECT_TX_PER_KB;
     o->push_chunk_bytes = PUSH_BUF_BYTES, o->push_chunk_rows = push_rows(BN, c_bf16);
     o->push_chunks_per_tile = C::A_ROWS / push_rows(BN, c_bf16);
     o->shared_memory_bytes = C::SMEM_BYTES;

@@ -102,8 +102,7 @@ typedef struct {
     int32_t tuning[2]; /* zero.  Measurement and test knobs: [0] bit 0 skips the loads, bit 1 the stores (results
                           are then meaningless), bits 2+3 make every in-kernel wait run out after 20 ms so that
                           the bounded-wait report can be tested, bit 4 makes cute_b200_gemm_tn_multi store to its
-                          destinations from registers instead of by TMA, bit 5 switches off (bit 6 forces) the
-                          per-tile start offset of the k loop that single-column problems get;
+                          destinations from registers instead of by TMA;
                           [1] row tiles walked per column step */
 } cute_b200_gemm_desc;
 
@@ -373,16 +372,18 @@ cute_b200_status cute_b200_device_status(uint32_t out[4]);
 typedef struct {
     uint32_t instruction_descriptor;
     uint32_t umma_m, umma_n, umma_k; /* shape of one tcgen05.mma over the CTA group */
-    uint32_t block_k;                /* k per ring stage */
+    uint32_t block_k;                /* k per k block: one 128-byte swizzle row of 16-bit values */
     uint32_t cta_rows;               /* rows of C per CTA */
-    uint32_t a_stage_bytes, b_stage_bytes, stage_bytes, stages;
+    uint32_t a_block_bytes, b_block_bytes; /* one k block of this CTA's rows of A / of B */
+    uint32_t k_blocks_per_stage;     /* k blocks behind one pair of full/empty barriers */
+    uint32_t stage_bytes, stages;
     uint32_t accumulator_halves;     /* 128-lane accumulators per CTA */
     uint32_t half_columns;           /* TMEM columns of one of them */
     uint32_t accumulator_buffers;    /* 2 = the epilogue overlaps the next tile's main loop */
     uint32_t tmem_columns;           /* allocated */
     uint32_t threads, epilogue_warps;
     uint32_t full_arrivals, empty_arrivals, tmem_full_arrivals, tmem_empty_arrivals;
-    uint32_t full_expect_tx_bytes;   /* announced per stage on the (leader's) full barrier */
+    uint32_t full_expect_tx_bytes_per_k_block; /* announced on the (leader's) full barrier for every k block a stage holds */
     uint32_t push_chunk_bytes, push_chunk_rows, push_chunks_per_tile;
     uint32_t shared_memory_bytes;
     uint32_t descriptor_k_step;      /* added to a descriptor's address field per umma_k */

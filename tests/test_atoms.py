@@ -207,10 +207,11 @@ def test_sm100_atoms_match_the_compiled_kernel(lib):
                 assert sw128_descriptor(0x4400 + 2 * info.umma_k) - sw128_descriptor(0x4400) == info.descriptor_k_step
                 # one stage = the A box and this CTA's share of the B box, 64 k each (one 128-byte swizzle row)
                 assert info.block_k * 2 == CopyOp.TmaLoad(rows=1).swizzle_bytes
-                assert info.a_stage_bytes == CopyOp.TmaLoad(rows=info.cta_rows).box_bytes
-                assert info.b_stage_bytes == CopyOp.TmaLoad(rows=tile_n // g).box_bytes
-                assert info.stage_bytes == info.a_stage_bytes + info.b_stage_bytes
-                assert info.full_expect_tx_bytes == g * info.stage_bytes
+                assert info.a_block_bytes == CopyOp.TmaLoad(rows=info.cta_rows).box_bytes
+                assert info.b_block_bytes == CopyOp.TmaLoad(rows=tile_n // g).box_bytes
+                assert info.stage_bytes == info.k_blocks_per_stage * (info.a_block_bytes + info.b_block_bytes)
+                assert info.full_expect_tx_bytes_per_k_block == g * (info.a_block_bytes + info.b_block_bytes)
+                assert info.k_blocks_per_stage in (1, 2, 4) and 16 * 1024 <= info.stage_bytes <= 64 * 1024
                 assert info.stages == min(192 * 1024 // info.stage_bytes, 12) and info.stages * info.stage_bytes <= 192 * 1024
                 assert info.cta_rows == tile_m and info.accumulator_halves == max(tile_m // 128, 1)
                 assert info.half_columns == op.tmem_columns
@@ -261,7 +262,7 @@ def test_sm100_shared_memory_layout():
     assert d & 0x3FFF == 0x440 and (d >> 16) & 0x3FFF == 1 and (d >> 32) & 0x3FFF == 64 and (d >> 46) & 3 == 1 and d >> 61 == 2
     assert sw128_descriptor(0x4400 + 32) - d == 2
     tma = CopyOp.TmaLoad(rows=256)
-    assert tma.box_bytes == 32768 and CopyOp.TmaLoad(rows=128).box_bytes + tma.box_bytes == 48 * 1024  # one 512x256 stage
+    assert tma.box_bytes == 32768 and CopyOp.TmaLoad(rows=128).box_bytes + tma.box_bytes == 48 * 1024  # one k block of the 512x256 tile
     # the pusher's chunk: BN columns of whole tile rows, 16 KiB per staging buffer, for bf16 and f32 C
     assert CopyOp.TmaStore(rows=32, cols=256, elem_bytes=2).box_bytes == 16384
     assert CopyOp.TmaStore(rows=16, cols=256, elem_bytes=4).box_bytes == 16384

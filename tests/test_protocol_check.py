@@ -5,8 +5,9 @@ import pytest
 
 from cute_rs_b200.check import ProtocolError, check_gemm, check_signal, tiling_from_library
 
-TILINGS = [dict(cta_group=g, stages=s, mh=mh, acc_bufs=ab) for g, s, mh, ab in
-           [(2, 4, 2, 1), (1, 3, 2, 1), (2, 7, 1, 2), (1, 4, 1, 2), (2, 9, 1, 2), (2, 5, 2, 2), (1, 7, 1, 2)]]
+TILINGS = [dict(cta_group=g, stages=s, mh=mh, acc_bufs=ab, kps=kps) for g, s, mh, ab, kps in
+           [(2, 4, 2, 1, 1), (1, 3, 2, 1, 1), (2, 7, 1, 2, 1), (1, 4, 1, 2, 1), (2, 9, 1, 2, 1), (2, 5, 2, 2, 1), (1, 7, 1, 2, 1),
+            (2, 3, 1, 2, 4), (1, 3, 1, 2, 2), (2, 4, 1, 2, 2)]]
 
 
 @pytest.mark.parametrize("tiling", TILINGS)
@@ -38,7 +39,7 @@ def test_wrong_barrier_constants_would_be_seen(lib):
     with pytest.raises(ProtocolError):
         check_gemm(units=(8, 8, 8), **dict(good, tmem_empty_arrivals=info.tmem_empty_arrivals // 2))
     with pytest.raises(ProtocolError):
-        check_gemm(units=(8, 8, 8), **dict(good, expect_tx=info.full_expect_tx_bytes // 2))
+        check_gemm(units=(8, 8, 8), **dict(good, expect_tx=info.full_expect_tx_bytes_per_k_block // 2))
     with pytest.raises(ProtocolError):
         check_gemm(units=(8, 8, 8), **dict(good, tmem_empty_arrivals=info.tmem_empty_arrivals + 1))
 
