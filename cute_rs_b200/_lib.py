@@ -30,7 +30,7 @@ EXPORTS = (
     "cute_b200_download", "cute_b200_free", "cute_b200_synchronize", "cute_b200_shard_rows",
     "cute_b200_gemm_tn_shard", "cute_b200_device_status", "cute_b200_launch_count", "cute_b200_alloc",
     "cute_b200_ipc_export", "cute_b200_ipc_open", "cute_b200_ipc_close", "cute_b200_copy_async", "cute_b200_gemm_tn_multi",
-    "cute_b200_gemm_layout_info", "cute_b200_comm_create", "cute_b200_comm_destroy", "cute_b200_comm_info",
+    "cute_b200_gemm_layout_info", "cute_b200_gemm_plan", "cute_b200_comm_create", "cute_b200_comm_destroy", "cute_b200_comm_info",
     "cute_b200_gemm_tn_sharded", "cute_b200_gemm_tn_sharded_host", "cute_b200_gemm_tn_multi_signal", "cute_b200_wait_signal",
 )
 
@@ -120,6 +120,7 @@ def load() -> ctypes.CDLL:
     L.cute_b200_gemm_tn_sharded.argtypes = [vp, ctypes.POINTER(GemmDesc), ctypes.POINTER(u64), ctypes.POINTER(u64),
                                             ctypes.POINTER(u64), i32]
     L.cute_b200_gemm_tn_sharded_host.argtypes = [vp, ctypes.POINTER(GemmDesc), vp, vp, vp, ctypes.POINTER(ctypes.c_double)]
+    L.cute_b200_gemm_plan.argtypes = [ctypes.POINTER(GemmDesc), i32, ctypes.POINTER(i32 * 4)]
     L.cute_b200_launch_count.argtypes = []
     L.cute_b200_launch_count.restype = u64
     for name in EXPORTS:
@@ -318,6 +319,13 @@ def gemm_layout_info(cta_group: int, tile_n: int, tile_m: int, ab_dtype: int = B
     out = GemmLayout()
     check(load().cute_b200_gemm_layout_info(cta_group, tile_n, tile_m, ab_dtype, c_dtype, smem_addr, ctypes.byref(out)))
     return out
+
+
+def gemm_plan(desc: GemmDesc, sm_count: int = 0) -> tuple:
+    """(cta_group, tile_n, tile_m, split_k) the library would run `desc` with."""
+    out = (ctypes.c_int32 * 4)()
+    check(load().cute_b200_gemm_plan(ctypes.byref(desc), sm_count, ctypes.byref(out)))
+    return tuple(out)
 
 
 # Every (cta_group, tile_n, tile_m) the library instantiates.

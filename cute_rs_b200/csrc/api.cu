@@ -118,6 +118,7 @@ static cute_b200_status read_status(uint32_t out[4]) {
         CB_CUDA(cudaMemcpy(out, static_word, 16, cudaMemcpyDeviceToHost));
         if (out[0] != 0) CB_CUDA(cudaMemset(static_word, 0, 16));
     }
+    if (out[0] != 0) gemm_tn_reset_counters();  // a kernel that gave up may have left tile counters half way
     return CUTE_B200_OK;
 }
 
@@ -822,6 +823,11 @@ cute_b200_status cute_b200_device_status(uint32_t out[4]) {
 cute_b200_status cute_b200_gemm_layout_info(int32_t cta_group, int32_t tile_n, int32_t tile_m, int32_t ab_dtype,
                                             int32_t c_dtype, uint32_t smem_addr, cute_b200_gemm_layout *out) {
     return gemm_layout_info(cta_group, tile_n, tile_m, ab_dtype, c_dtype, smem_addr, out);
+}
+
+cute_b200_status cute_b200_gemm_plan(const cute_b200_gemm_desc *desc, int32_t sm_count, int32_t out[4]) {
+    if (!desc || !out) return fail(CUTE_B200_ERR_NULL_POINTER, "gemm_plan: null argument");
+    return gemm_plan(*desc, sm_count, out);
 }
 
 uint64_t cute_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }

@@ -79,6 +79,23 @@ def test_sharded_launcher_checks_its_arguments_without_a_device(lib):
         assert e.value.status == lib.ERR_NO_DEVICE
 
 
+def test_tiling_choices_for_the_benchmark_shapes(lib):
+    """The cost model's picks for the configurations of the runtime_gemm sweep, pinned: each was
+    measured to be the fastest tiling for its shape (a change of the model that moves one of them has
+    to be deliberate)."""
+    plan = lambda m, n, k, **kw: lib.gemm_plan(lib.gemm_desc(m, n, k, lib.BF16, lib.BF16, **kw))
+    assert plan(8192, 8192, 8192) == (2, 256, 256, 1)          # the 512 x 256 pair tile
+    assert plan(32768, 32768, 8192) == (2, 256, 256, 1)
+    assert plan(4096, 32768, 8192) == (2, 256, 256, 1)         # one rank's block of the sharded workload
+    assert plan(4096, 4096, 4096) == (2, 256, 256, 1)
+    assert plan(16384, 1024, 8192) == (2, 256, 256, 1)
+    assert plan(2048, 2048, 2048) == (1, 256, 128, 1)          # one wave of single CTAs
+    assert plan(1024, 1024, 1024) == (1, 128, 128, 1)
+    assert plan(8192, 128, 8192) == (2, 128, 64, 1)            # few row tiles, long k: the 64-row pair tile, one kernel
+    assert plan(8192, 128, 8192, split_k=4)[3] == 4 and plan(8192, 128, 64, split_k=4)[3] == 1  # honoured, cut to the k blocks
+    assert plan(256, 256, 256, tile_m=64)[:3] == (2, 128, 64) or plan(256, 256, 256, tile_m=64)[0] == 2
+
+
 def test_argument_checks_come_before_the_device(lib):
     # check_launch runs before any CUDA call (src/cuda.rs:452), so its
     # messages can be compared without a GPU.
