@@ -118,7 +118,6 @@ static cute_b200_status read_status(uint32_t out[4]) {
         CB_CUDA(cudaMemcpy(out, static_word, 16, cudaMemcpyDeviceToHost));
         if (out[0] != 0) CB_CUDA(cudaMemset(static_word, 0, 16));
     }
-    if (out[0] != 0) gemm_tn_reset_counters();  // a kernel that gave up may have left tile counters half way
     return CUTE_B200_OK;
 }
 

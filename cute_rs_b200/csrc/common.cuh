@@ -64,7 +64,6 @@ cute_b200_status gemm_layout_info(int cta_group, int tile_n, int tile_m, int ab_
 cute_b200_status gemm_plan(const cute_b200_gemm_desc &desc, int sm_count, int32_t out[4]);
 cute_b200_status gemm_tn_init(const DeviceState &dev);
 void gemm_tn_release_scratch();
-void gemm_tn_reset_counters();
 cute_b200_status gemm_tn_static(const cute_b200_gemm_desc &desc, uint64_t a, uint64_t b, uint64_t c, cudaStream_t stream,
                                 uint32_t *shared_status);
 // Device address of the status words gemm_tn_static owns on `device`, null until that entry point has run there.

@@ -75,9 +75,6 @@ enum : uint32_t {
     WHERE_SIGNAL = 7  // cute_b200_wait_signal: the counter did not reach the expected value in time
 };
 
-#ifndef CB_FENCE_AFTER_FULL
-#define CB_FENCE_AFTER_FULL 0  // 1 puts a tcgen05.fence::after_thread_sync behind every wait for a stage's loads (measurements)
-#endif
 #ifndef CB_FAST_DRAIN
 #define CB_FAST_DRAIN 1  // 0 builds the epilogue without the read-everything-then-store path (measurements)
 #endif
@@ -153,14 +150,6 @@ struct GemmParams {
                    // producer issue nothing at all (every consumer wait then runs out), bit 3 shortens the limit
     int splits;              // k is cut into this many ranges, one work unit each (1 = no split)
     size_t split_stride;     // bytes between the partial-sum planes of consecutive ranges
-    // Summing the planes inside the kernel: every (tile, CTA of the group, epilogue warp) has a counter,
-    // zero between launches; a warp that has stored its part of a plane adds 1, and the one that brings
-    // the counter to `splits` adds that part of the planes in ascending order, applies the epilogue and
-    // writes it to `final_c`.
-    uint32_t *tile_counters;  // null: the planes are summed by a second kernel
-    void *final_c;
-    int final_ldc, final_bf16;
-    float final_alpha, final_beta;
     uint32_t *status;
     // Further copies of C that receive the same result (other GPUs' C over NVLink peer mappings).
     // Plain epilogue, no k split.  push = 1: the pusher warp copies every finished tile from C to
@@ -478,14 +467,7 @@ __global__ void __launch_bounds__(num_threads(BN, MH), 1)
                         ok = false;
                         break;
                     }
-                    // No tcgen05.fence here: the loads' bytes were counted on the barrier this thread has just
-                    // waited for, which is all an MMA needs to read them.  (A fence at this point holds the
-                    // next MMA back until the tensor core has drained what is queued: about 130 clocks per
-                    // stage with the pipe idle.  The fence is needed, and kept, where another thread's
-                    // tcgen05.ld has to be ordered before this thread's MMAs: behind the wait for a TMEM half.)
-#if CB_FENCE_AFTER_FULL
                     ptx::tc_fence_after();
-#endif
                     const uint32_t stage = ring + uint32_t(s) * C::STAGE_BYTES;
 #pragma unroll
                     for (int kk = 0; kk < C::KPS; kk++) {
@@ -657,55 +639,6 @@ __global__ void __launch_bounds__(num_threads(BN, MH), 1)
 #if CB_FAST_DRAIN
         tile_stored:
 #endif
-            if (p.tile_counters != nullptr) {
-                // k was split: this warp's part of the range's plane is stored.  The same warp of the CTAs
-                // that work on the tile's other ranges stores the same rows and columns of their planes, so
-                // the count is kept per warp: whichever of them comes last sums that part of all planes
-                // (they are in L2 by now) and writes it to C.  No warp waits for another.
-                __threadfence();
-                __syncwarp();
-                uint32_t *counter = p.tile_counters + size_t(u.tile * CTA_GROUP + int(rank)) * (4 * EG) + (warp - 2);
-                uint32_t last = 0u;
-                if (lane == 0) last = (atomicAdd(counter, 1u) + 1u == uint32_t(p.splits)) ? 1u : 0u;
-                last = __shfl_sync(0xffffffffu, last, 0);
-                if (last != 0u) {
-                    __threadfence();
-#pragma unroll 1
-                    for (int i = 0; i < ITEMS; i++) {
-                        const int r = row0 + (i / CH) * BM, c0 = col_base + col_of(i);
-                        if (r >= p.M || c0 >= p.N) continue;
-                        const int ncol = p.N - c0 < 32 ? p.N - c0 : 32;
-                        const float *plane = reinterpret_cast<const float *>(p.C) + size_t(r) * p.ldc + c0;
-                        const size_t stride = p.split_stride / 4;
-                        float acc[32];
-#pragma unroll
-                        for (int j = 0; j < 32; j++) acc[j] = j < ncol ? __ldcg(plane + j) : 0.0f;
-                        for (int sp = 1; sp < p.splits; sp++) {
-#pragma unroll
-                            for (int j = 0; j < 32; j++)
-                                if (j < ncol) acc[j] = __fadd_rn(acc[j], __ldcg(plane + size_t(sp) * stride + j));
-                        }
-                        const bool fplain = (p.final_alpha == 1.0f && p.final_beta == 0.0f);
-                        if (p.final_bf16) {
-                            __nv_bfloat16 *out = reinterpret_cast<__nv_bfloat16 *>(p.final_c) + size_t(r) * p.final_ldc + c0;
-#pragma unroll
-                            for (int j = 0; j < 32; j++)
-                                if (j < ncol) {
-                                    const float v = fplain ? acc[j]
-                                                           : __fadd_rn(__fmul_rn(p.final_alpha, acc[j]), __fmul_rn(p.final_beta, __bfloat162float(out[j])));
-                                    out[j] = __float2bfloat16_rn(v);
-                                }
-                        } else {
-                            float *out = reinterpret_cast<float *>(p.final_c) + size_t(r) * p.final_ldc + c0;
-#pragma unroll
-                            for (int j = 0; j < 32; j++)
-                                if (j < ncol) out[j] = fplain ? acc[j] : __fadd_rn(__fmul_rn(p.final_alpha, acc[j]), __fmul_rn(p.final_beta, out[j]));
-                        }
-                    }
-                    __syncwarp();
-                    if (lane == 0) *counter = 0u;  // zero again for the next launch
-                }
-            }
             if (p.push) {
                 // This warp's part of the tile is in C: make the stores visible to the TMA unit
                 // (async proxy) and publish the warp's tile count for the pusher.
@@ -1099,10 +1032,8 @@ double choose_tiling(int m, int n, int k, int c_bytes, int sm_count, int want_gr
 // stream.  `idle` is recorded behind the second pass of each split GEMM and the
 // next split GEMM's stream waits for it before its first pass, so two calls on
 // different streams take turns on the planes instead of racing.
-constexpr size_t kCounterBytes = 256 * 1024;  // counters of the in-kernel summation, in front of the planes
-constexpr size_t kMaxCounters = kCounterBytes / 4;
 struct Scratch {
-    void *ptr = nullptr;  // [counters, zero between launches][planes]
+    void *ptr = nullptr;
     size_t size = 0;
     cudaEvent_t idle = nullptr;
 };
@@ -1112,8 +1043,7 @@ std::mutex g_scratch_mu;
 // Hands out the device's scratch (grown if needed) after making `stream` wait
 // for the previous user.  The caller queues its kernels and then calls
 // scratch_release on the same stream.
-cute_b200_status scratch_acquire(size_t plane_bytes, cudaStream_t stream, void **out, uint32_t **counters) {
-    const size_t bytes = kCounterBytes + plane_bytes;
+cute_b200_status scratch_acquire(size_t bytes, cudaStream_t stream, void **out) {
     int device = 0;
     CB_CUDA(cudaGetDevice(&device));
     if (device < 0 || device >= 64) return fail(CUTE_B200_ERR_NO_DEVICE, "no current device");
@@ -1125,12 +1055,10 @@ cute_b200_status scratch_acquire(size_t plane_bytes, cudaStream_t stream, void *
         sc.ptr = nullptr;
         sc.size = 0;
         CB_CUDA(cudaMalloc(&sc.ptr, bytes));
-        CB_CUDA(cudaMemset(sc.ptr, 0, kCounterBytes));
         sc.size = bytes;
     }
     CB_CUDA(cudaStreamWaitEvent(stream, sc.idle, 0));  // an event never recorded counts as complete
-    *counters = static_cast<uint32_t *>(sc.ptr);
-    *out = static_cast<char *>(sc.ptr) + kCounterBytes;
+    *out = sc.ptr;
     return CUTE_B200_OK;
 }
 
@@ -1150,14 +1078,12 @@ cute_b200_status scratch_release(cudaStream_t stream) {
 constexpr size_t kStaticScratchBytes = size_t(32) << 20;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 static __device__ __align__(16) uint32_t g_static_status[4];
-static __device__ __align__(16) uint32_t g_static_counters[kMaxCounters];  // zero between launches, like the allocated ones
 
 namespace {
 struct StaticSetup {
     bool ready = false;
     void *scratch = nullptr;      // device address of g_static_scratch on this device
     uint32_t *status = nullptr;   // device address of g_static_status on this device
-    uint32_t *counters = nullptr; // device address of g_static_counters on this device
     int sm_count = 0;
 };
 StaticSetup g_static_setup[64];
@@ -1180,8 +1106,6 @@ cute_b200_status static_setup(int device, StaticSetup **out) {
         st.scratch = p;
         CB_CUDA(cudaGetSymbolAddress(&p, g_static_status));
         st.status = static_cast<uint32_t *>(p);
-        CB_CUDA(cudaGetSymbolAddress(&p, g_static_counters));
-        st.counters = static_cast<uint32_t *>(p);
 #define CB_SET(G, N_, H, BF) CB_TRY((set_smem_limit<G, N_, H, BF>()));
         CB_GEMM_VARIANTS(CB_SET)
 #undef CB_SET
@@ -1191,9 +1115,6 @@ cute_b200_status static_setup(int device, StaticSetup **out) {
     return CUTE_B200_OK;
 }
 }  // namespace
-
-static void use_tile_counters(GemmParams &q, uint32_t *counters, const cute_b200_gemm_desc &d, int group, int bn, int cta_rows,
-                              uint64_t c, bool c_bf16);
 
 uint32_t *gemm_tn_static_status_words(int device) {
     if (device < 0 || device >= 64) return nullptr;
@@ -1259,8 +1180,6 @@ cute_b200_status gemm_tn_static(const cute_b200_gemm_desc &d, uint64_t a, uint64
     const int cta_rows = mh == 0 ? 64 : BM * mh;
     p.idesc = make_idesc(d.ab_dtype == CUTE_B200_BF16, (mh == 0 ? 64 : BM) * group, bn);
 
-    use_tile_counters(p, setup->counters, d, group, bn, cta_rows, c, c_bf16);
-
     CUtensorMap tmA, tmB;
     CB_TRY(make_tensor_map(&tmA, a, d.ab_dtype, d.m, d.k, cta_rows));
     CB_TRY(make_tensor_map(&tmB, b, d.ab_dtype, d.n, d.k, bn / group));
@@ -1270,7 +1189,6 @@ cute_b200_status gemm_tn_static(const cute_b200_gemm_desc &d, uint64_t a, uint64
     CB_GEMM_VARIANTS(CB_CASE)
 #undef CB_CASE
     CB_TRY(st);
-    if (p.tile_counters) return CUTE_B200_OK;  // the kernel has summed the planes itself
     const unsigned blocks = unsigned((plane + 1023) / 1024);
     if (c_bf16)
         gemm_splitk_reduce<true><<<blocks, 256, 0, stream>>>(static_cast<const float *>(setup->scratch), splits, plane, plane,
@@ -1281,32 +1199,6 @@ cute_b200_status gemm_tn_static(const cute_b200_gemm_desc &d, uint64_t a, uint64
     CB_CUDA(cudaGetLastError());
     count_launch();
     return CUTE_B200_OK;
-}
-
-// The planes are summed inside the kernel when every (tile, CTA of the group) gets a counter.
-static void use_tile_counters(GemmParams &q, uint32_t *counters, const cute_b200_gemm_desc &d, int group, int bn, int cta_rows,
-                              uint64_t c, bool c_bf16) {
-    const long long tile_rows = (long long)cta_rows * group;
-    const long long tiles = ((d.m + tile_rows - 1) / tile_rows) * ((d.n + bn - 1) / bn);
-    if (tiles * group * 16 > (long long)kMaxCounters || (d.tuning[0] & 32)) return;  // tuning bit 5: keep the second kernel (measurements)
-    q.tile_counters = counters;
-    q.final_c = reinterpret_cast<void *>(c);
-    q.final_ldc = d.n;
-    q.final_bf16 = c_bf16 ? 1 : 0;
-    q.final_alpha = d.alpha;
-    q.final_beta = d.beta;
-}
-
-// After a kernel gave up, counters of tiles it did not finish are left non-zero: zero them all.
-void gemm_tn_reset_counters() {
-    int device = 0;
-    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return;
-    {
-        std::lock_guard<std::mutex> lock(g_scratch_mu);
-        if (g_scratch[device].ptr) cudaMemset(g_scratch[device].ptr, 0, kCounterBytes);
-    }
-    std::lock_guard<std::mutex> lock(g_static_mu);
-    if (g_static_setup[device].ready) cudaMemset(g_static_setup[device].counters, 0, kCounterBytes);
 }
 
 void gemm_tn_release_scratch() {
@@ -1485,11 +1377,9 @@ static cute_b200_status gemm_tn_ex(const cute_b200_gemm_desc &d, uint64_t a, uin
         // epilogue.  The scratch is allocated on first need and kept.
         const size_t plane = size_t(d.m) * d.n;
         void *scratch = nullptr;
-        uint32_t *counters = nullptr;
-        CB_TRY(scratch_acquire(plane * 4 * splits, stream, &scratch, &counters));
+        CB_TRY(scratch_acquire(plane * 4 * splits, stream, &scratch));
         GemmParams q = p;
         q.C = scratch;
-        use_tile_counters(q, counters, d, group, bn, cta_rows, c, c_bf16);
         q.alpha = 1.0f;
         q.beta = 0.0f;
         q.split_stride = plane * 4;
@@ -1500,7 +1390,6 @@ static cute_b200_status gemm_tn_ex(const cute_b200_gemm_desc &d, uint64_t a, uin
         CB_GEMM_VARIANTS(CB_CASE)
 #undef CB_CASE
         CB_TRY(st);
-        if (q.tile_counters) return scratch_release(stream);  // the kernel has summed the planes itself
         const unsigned blocks = unsigned((plane + 1023) / 1024);
         if (c_bf16)
             gemm_splitk_reduce<true><<<blocks, 256, 0, stream>>>(static_cast<const float *>(scratch), splits, plane, plane,

@@ -93,19 +93,17 @@ typedef struct {
     int32_t cta_group; /* 0 = choose; 1 = one CTA per tile; 2 = a CTA pair shares each tile's MMAs */
     int32_t tile_m;    /* rows of C per CTA: 0 = choose; 128 or 256; 64 = the pair tile for few row tiles and a long
                           k (needs cta_group 0 or 2): 16 KiB stages, a 12-deep ring */
-    int32_t split_k;   /* k ranges computed as separate work units, each writing an f32 plane of partial sums into a
-                          scratch buffer the library allocates on first need; the planes are added in ascending
-                          order and the epilogue applied by whichever CTA finishes a tile's last range (inside the
-                          same kernel; a second kernel only for problems of more than 4096 tile-CTAs): 0 = choose,
-                          1 = never, 2..16 = exactly that many (cut down to the number of 64-wide k blocks when k
-                          is shorter; ranges left without a block contribute zeros).  The scratch is one buffer per
-                          device shared by all streams: the library orders split launches on different streams
-                          one behind the other with an event, so they do not race, but they do not overlap either */
+    int32_t split_k;   /* k ranges computed as separate work units and summed in ascending order by a second kernel
+                          through an f32 scratch buffer the library allocates on first need: 0 = choose, 1 = never,
+                          2..16 = exactly that many (cut down to the number of 64-wide k blocks when k is shorter;
+                          ranges left without a block contribute zeros).  The scratch is one buffer per device shared
+                          by all streams: the library orders split launches on different streams one behind the
+                          other with an event, so they do not race, but they do not overlap either */
     int32_t tuning[2]; /* zero.  Measurement and test knobs: [0] bit 0 skips the loads, bit 1 the stores (results
                           are then meaningless), bits 2+3 make every in-kernel wait run out after 20 ms so that
                           the bounded-wait report can be tested, bit 4 makes cute_b200_gemm_tn_multi store to its
-                          destinations from registers instead of by TMA, bit 5 makes a split-k GEMM sum its planes with a
-                          second kernel; [1] row tiles walked per column step */
+                          destinations from registers instead of by TMA;
+                          [1] row tiles walked per column step */
 } cute_b200_gemm_desc;
 
 cute_b200_status cute_b200_gemm_tn(const cute_b200_gemm_desc *desc, uint64_t dA, uint64_t dB, uint64_t dC,

@@ -480,32 +480,6 @@ def test_gemm_split_k_random_within_bound(lib, gpu):
         assert (np.abs(got.astype(np.float64) - want) <= allowed).all()
 
 
-@pytest.mark.parametrize("m,n,k,split_k,tile_m,cta_group", [(1024, 384, 2048, 4, 0, 0), (8192, 128, 2048, 2, 128, 1), (700, 200, 1600, 6, 64, 2),
-                                                          (512, 512, 4096, 16, 256, 2)])
-def test_gemm_split_k_summed_in_the_kernel_equals_the_second_kernel(lib, gpu, m, n, k, split_k, tile_m, cta_group):
-    """The planes of a split GEMM are summed by whichever warp finishes its part of a tile's last range;
-    with tuning bit 5 a second kernel sums them instead.  Same ranges, same ascending order: same bits, on
-    data that rounds, for f32 and bf16 C and a non-trivial epilogue; and the counters are back at zero, so
-    that a second call gives the same again."""
-    import torch
-    a, b, c = lcg_buffers([m * k, n * k, m * n], small=False)
-    a_bits, b_bits = oracle.f32_to_bf16_bits(a.reshape(m, k)), oracle.f32_to_bf16_bits(b.reshape(n, k))
-    dA, dB = dev(a_bits.view(np.int16)), dev(b_bits.view(np.int16))
-    for cdt, c0 in ((lib.F32, c.reshape(m, n)), (lib.BF16, oracle.f32_to_bf16_bits(c.reshape(m, n)).view(np.int16))):
-        outs = []
-        for knob in (0, 32, 0):
-            dC = dev(c0.copy())
-            d = lib.gemm_desc(m, n, k, lib.BF16, cdt, 1.5, -0.5, tile_m=tile_m, cta_group=cta_group, split_k=split_k)
-            d.tuning[0] = knob
-            before = lib.launch_count()
-            lib.gemm_tn(d, dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), 0)
-            torch.cuda.synchronize()
-            assert lib.launch_count() - before == (2 if knob else 1)
-            outs.append(dC.cpu().numpy())
-        assert lib.device_status() == (0, 0, 0, 0)
-        assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[0], outs[2])
-
-
 def test_gemm_split_k_on_two_streams_takes_turns(lib, gpu):
     """Split GEMMs share one scratch buffer per device.  Two of them queued on
     different streams (a skinny shape the library splits by itself, and a forced
