@@ -279,7 +279,9 @@ cute_b200_status comm_info(void *p, int32_t out[4]) {
     Comm *comm = as_comm(p);
     if (!comm || !out) return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "comm_info: not a communicator of this library, or null output");
     std::lock_guard<std::mutex> lock(comm->call_mu);
-    const bool nccl = ensure_nccl(*comm) == CUTE_B200_OK;
+    // "usable" = the library loads and the devices are distinct; its communicators are only made by the first
+    // call that needs them (ncclCommInitAll takes seconds and talks to every GPU)
+    const bool nccl = comm->nccl_ok || (!comm->nccl_tried && comm->distinct && comm->nccl.load());
     out[0] = comm->n, out[1] = comm->distinct ? 1 : 0, out[2] = comm->peers_ok ? 1 : 0, out[3] = nccl ? 1 : 0;
     return CUTE_B200_OK;
 }

@@ -306,7 +306,7 @@ cute_b200_status cute_b200_wait_signal(uint64_t dSignals, uint32_t mask, uint32_
  * A device may be named more than once (its blocks are then computed one after
  * the other on that device; useful to run a partition meant for more GPUs than
  * are present).  cute_b200_comm_info: out = {ngpus, all devices distinct, peer
- * access between every pair, collective library usable}.
+ * access between every pair, collective library loadable}.
  *
  * cute_b200_gemm_tn_sharded (device buffers, one pointer per GPU, each in that
  * GPU's memory): dA_shard[g] = GPU g's rows of A, dB[g] = all of B.  With
