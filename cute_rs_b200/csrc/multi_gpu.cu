@@ -422,7 +422,17 @@ cute_b200_status gemm_tn_sharded_host(void *p, const cute_b200_gemm_desc *desc, 
             CB_CUDA(cudaEventRecord(gs.b_spread, gs.spread[1]));
             return CUTE_B200_OK;
         };
+#ifdef CB_TRACE_SHARDED
+        cudaEvent_t tr[8];
+        for (auto &e : tr) cudaEventCreate(&e);
+        const auto host_p2 = std::chrono::steady_clock::now();
+        cudaEventRecord(tr[0], gs.up);
+#endif
         st = phase2();
+#ifdef CB_TRACE_SHARDED
+        cudaEventRecord(tr[1], gs.up);         // B share is up
+        cudaEventRecord(tr[2], gs.spread[1]);  // and with every peer
+#endif
         if (!comm->barrier.arrive(st == CUTE_B200_OK)) {
             cudaDeviceSynchronize();
             return st != CUTE_B200_OK ? st : fail(CUTE_B200_ERR_CUDA, "another GPU of the call failed");
@@ -454,13 +464,32 @@ cute_b200_status gemm_tn_sharded_host(void *p, const cute_b200_gemm_desc *desc, 
                                reinterpret_cast<uint64_t>(dC + size_t(r0) * c_pitch), gs.compute, *dev));
                 CB_CUDA(cudaEventRecord(gs.c_done[i], gs.compute));
                 CB_CUDA(cudaStreamWaitEvent(gs.down, gs.c_done[i], 0));
+#ifdef CB_TRACE_SHARDED
+                if (i == 0) cudaEventRecord(tr[3], gs.compute), cudaEventRecord(tr[4], gs.down);  // first product done, first way down begins
+#endif
                 CB_CUDA(cudaMemcpyAsync(static_cast<char *>(hC) + grow0 * c_pitch, dC + size_t(r0) * c_pitch, size_t(r) * c_pitch,
                                         cudaMemcpyDeviceToHost, gs.down));
             }
             return CUTE_B200_OK;
         };
         st = phase3();
-        const cute_b200_status sync = sync_and_check();  // everything queued reads or writes the caller's buffers
+#ifdef CB_TRACE_SHARDED
+        cudaEventRecord(tr[5], gs.up);
+        cudaEventRecord(tr[6], gs.compute);
+        cudaEventRecord(tr[7], gs.down);
+#endif
+        const cute_b200_status sync = sync_and_check();
+#ifdef CB_TRACE_SHARDED
+        {
+            float ms[8] = {};
+            for (int i = 1; i < 8; i++) cudaEventElapsedTime(&ms[i], tr[0], tr[i]);
+            const double h0 = std::chrono::duration<double, std::milli>(host_p2 - t_start).count();
+            const double h1 = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t_start).count();
+            fprintf(stderr, "trace gpu %d: host->phase2 %.2f | B up %.2f spread %.2f gemm0 %.2f d2h0-start %.2f A-up-all %.2f gemm-all %.2f d2h-all %.2f | host end %.2f ms\n",
+                    g, h0, ms[1], ms[2], ms[3], ms[4], ms[5], ms[6], ms[7], h1);
+            for (auto &e : tr) cudaEventDestroy(e);
+        }
+#endif  // everything queued reads or writes the caller's buffers
         // nobody's B may be overwritten by the next call while a slower GPU still multiplies: leave together
         comm->barrier.arrive(true);
         return st != CUTE_B200_OK ? st : sync;
