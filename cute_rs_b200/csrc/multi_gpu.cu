@@ -32,6 +32,7 @@ namespace {
 constexpr uint32_t kCommMagic = 0xC0B200C0u;
 constexpr int kMaxGpus = 8;
 constexpr int kMaxPanels = 16;
+constexpr int kMaxBlocks = 8;  // column blocks of C in the host-buffer call (B goes up block by block)
 
 // The few entry points of the collective library that the fallback needs, resolved at run time.
 struct Nccl {
@@ -95,7 +96,7 @@ private:
 struct GpuState {
     int ordinal = 0;
     cudaStream_t compute = nullptr, up = nullptr, down = nullptr, spread[2] = {nullptr, nullptr};
-    cudaEvent_t b_up = nullptr, spread_join = nullptr, b_spread = nullptr, a_up[kMaxPanels] = {}, c_done[kMaxPanels] = {};
+    cudaEvent_t b_up[kMaxBlocks] = {}, spread_join[kMaxBlocks] = {}, b_spread[kMaxBlocks] = {}, a_up[kMaxPanels] = {}, c_done = nullptr;
     void *buf[3] = {nullptr, nullptr, nullptr};  // staging of the host-buffer call: A rows, B, C rows
     size_t bytes[3] = {0, 0, 0};
 };
@@ -226,13 +227,13 @@ cute_b200_status comm_create(int ngpus, const int *ordinals, void **comm_out) {
             CB_CUDA(cudaStreamCreateWithFlags(&gs.up, cudaStreamNonBlocking));
             CB_CUDA(cudaStreamCreateWithFlags(&gs.down, cudaStreamNonBlocking));
             for (auto &s : gs.spread) CB_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
-            CB_CUDA(cudaEventCreateWithFlags(&gs.b_up, cudaEventDisableTiming));
-            CB_CUDA(cudaEventCreateWithFlags(&gs.b_spread, cudaEventDisableTiming));
-            CB_CUDA(cudaEventCreateWithFlags(&gs.spread_join, cudaEventDisableTiming));
-            for (int i = 0; i < kMaxPanels; i++) {
-                CB_CUDA(cudaEventCreateWithFlags(&gs.a_up[i], cudaEventDisableTiming));
-                CB_CUDA(cudaEventCreateWithFlags(&gs.c_done[i], cudaEventDisableTiming));
+            for (int j = 0; j < kMaxBlocks; j++) {
+                CB_CUDA(cudaEventCreateWithFlags(&gs.b_up[j], cudaEventDisableTiming));
+                CB_CUDA(cudaEventCreateWithFlags(&gs.b_spread[j], cudaEventDisableTiming));
+                CB_CUDA(cudaEventCreateWithFlags(&gs.spread_join[j], cudaEventDisableTiming));
             }
+            for (int i = 0; i < kMaxPanels; i++) CB_CUDA(cudaEventCreateWithFlags(&gs.a_up[i], cudaEventDisableTiming));
+            CB_CUDA(cudaEventCreateWithFlags(&gs.c_done, cudaEventDisableTiming));
         }
         return CUTE_B200_OK;
     };
@@ -260,12 +261,12 @@ cute_b200_status comm_destroy(void *p) {
         if (comm->nccl_ok && comm->nccl_comm[g]) comm->nccl.CommDestroy(comm->nccl_comm[g]);
         for (cudaStream_t s : {gs.compute, gs.up, gs.down, gs.spread[0], gs.spread[1]})
             if (s) cudaStreamDestroy(s);
-        for (cudaEvent_t e : {gs.b_up, gs.b_spread, gs.spread_join})
-            if (e) cudaEventDestroy(e);
-        for (int i = 0; i < kMaxPanels; i++) {
+        for (int j = 0; j < kMaxBlocks; j++)
+            for (cudaEvent_t e : {gs.b_up[j], gs.b_spread[j], gs.spread_join[j]})
+                if (e) cudaEventDestroy(e);
+        for (int i = 0; i < kMaxPanels; i++)
             if (gs.a_up[i]) cudaEventDestroy(gs.a_up[i]);
-            if (gs.c_done[i]) cudaEventDestroy(gs.c_done[i]);
-        }
+        if (gs.c_done) cudaEventDestroy(gs.c_done);
         for (void *b : gs.buf)
             if (b) cudaFree(b);
     }
@@ -387,11 +388,21 @@ cute_b200_status gemm_tn_sharded_host(void *p, const cute_b200_gemm_desc *desc, 
     const int n = comm->n;
     const size_t esize = c_elem_bytes(*desc), c_pitch = size_t(desc->n) * esize, k_bytes = size_t(desc->k) * 2;
     const bool reads_c = !(desc->alpha == 1.0f && desc->beta == 0.0f);
-    int begin[kMaxGpus], rows[kMaxGpus], b_begin[kMaxGpus], b_rows[kMaxGpus];
-    for (int g = 0; g < n; g++) {
-        CB_TRY(cute_b200_shard_rows(desc->m, n, g, &begin[g], &rows[g]));
-        CB_TRY(cute_b200_shard_rows(desc->n, n, g, &b_begin[g], &b_rows[g]));  // the share of B this GPU uploads
-    }
+    int begin[kMaxGpus], rows[kMaxGpus];
+    for (int g = 0; g < n; g++) CB_TRY(cute_b200_shard_rows(desc->m, n, g, &begin[g], &rows[g]));
+    // The way down to the host is the slowest leg (every GPU sends m/N x n elements of C back against
+    // m/N + n/N rows of k elements that it fetches, and the host takes writes from several GPUs more
+    // slowly than it serves their reads), so it should start as early as possible and never wait.  C is
+    // cut into blocks of columns and B goes up block by block: of block j every GPU fetches 1/N of the
+    // rows of B and passes them to the others over NVLink.  The first block is multiplied panel by panel
+    // of A's rows as they arrive, the later ones against all of this GPU's rows at once, and every
+    // finished block of C goes down while the uploads and products of the next ones run ahead.
+    int blocks = desc->k > 0 ? desc->n / 4096 : 1;
+    blocks = blocks < 1 ? 1 : (blocks > kMaxBlocks ? kMaxBlocks : blocks);
+    int col0[kMaxBlocks + 1];
+    for (int j = 0; j <= blocks; j++) col0[j] = j == blocks ? desc->n : int(int64_t(desc->n) * j / blocks / 256 * 256);
+    // rows [piece(j, g), piece(j, g + 1)) of B: what GPU g fetches of block j
+    auto piece = [&](int j, int g) { return col0[j] + int(int64_t(col0[j + 1] - col0[j]) * g / n); };
     const cute_b200_status st = on_every_gpu(*comm, [&](int g) -> cute_b200_status {
         GpuState &gs = comm->gpu[g];
         DeviceState *dev = nullptr;
@@ -402,73 +413,107 @@ cute_b200_status gemm_tn_sharded_host(void *p, const cute_b200_gemm_desc *desc, 
         if (st == CUTE_B200_OK) st = grow(gs, 2, size_t(rows[g]) * c_pitch);
         if (!comm->barrier.arrive(st == CUTE_B200_OK)) return st != CUTE_B200_OK ? st : fail(CUTE_B200_ERR_CUDA, "another GPU of the call failed");
 
-        // phase 2: this GPU's share of B goes up from the host and on to every other GPU over NVLink
         char *dA = static_cast<char *>(gs.buf[0]), *dB = static_cast<char *>(gs.buf[1]), *dC = static_cast<char *>(gs.buf[2]);
-        auto phase2 = [&]() -> cute_b200_status {
-            if (desc->k > 0 && b_rows[g] > 0) {
-                const size_t off = size_t(b_begin[g]) * k_bytes, bytes = size_t(b_rows[g]) * k_bytes;
-                CB_CUDA(cudaMemcpyAsync(dB + off, static_cast<const char *>(hB) + off, bytes, cudaMemcpyHostToDevice, gs.up));
-                CB_CUDA(cudaEventRecord(gs.b_up, gs.up));
-                for (auto &s : gs.spread) CB_CUDA(cudaStreamWaitEvent(s, gs.b_up, 0));
-                for (int s = 1; s < n; s++) {  // two streams, so that two copy engines and two links work at a time
-                    const int peer = (g + s) % n;
-                    CB_CUDA(cudaMemcpyPeerAsync(static_cast<char *>(comm->gpu[peer].buf[1]) + off, comm->gpu[peer].ordinal,
-                                                dB + off, gs.ordinal, bytes, gs.spread[s & 1]));
-                }
-            }
-            // b_spread: this GPU's share of B is in its own memory and in every peer's
-            CB_CUDA(cudaEventRecord(gs.spread_join, gs.spread[0]));
-            CB_CUDA(cudaStreamWaitEvent(gs.spread[1], gs.spread_join, 0));
-            CB_CUDA(cudaEventRecord(gs.b_spread, gs.spread[1]));
-            return CUTE_B200_OK;
-        };
+        int panels = 8;
+        while (panels > 1 && (rows[g] / panels < 256 || size_t(rows[g] / panels) * c_pitch < (size_t(4) << 20))) panels /= 2;
+        const int per = rows[g] > 0 ? ((rows[g] + panels - 1) / panels + 127) / 128 * 128 : 128;
+        panels = (rows[g] + per - 1) / per;
 #ifdef CB_TRACE_SHARDED
         cudaEvent_t tr[8];
         for (auto &e : tr) cudaEventCreate(&e);
         const auto host_p2 = std::chrono::steady_clock::now();
         cudaEventRecord(tr[0], gs.up);
 #endif
+        // phase 2: everything that goes up, in the order in which it unlocks blocks of C: the first
+        // panel of A, this GPU's piece of the first block of B, the other panels of A, the other pieces
+        // of B.  Every piece of B goes on to every other GPU as soon as it is here.
+        auto b_piece = [&](int j) -> cute_b200_status {
+            const int r0 = piece(j, g), r1 = piece(j, g + 1);
+            if (desc->k > 0 && r1 > r0) {
+                const size_t off = size_t(r0) * k_bytes, bytes = size_t(r1 - r0) * k_bytes;
+                CB_CUDA(cudaMemcpyAsync(dB + off, static_cast<const char *>(hB) + off, bytes, cudaMemcpyHostToDevice, gs.up));
+                CB_CUDA(cudaEventRecord(gs.b_up[j], gs.up));
+                for (auto &s : gs.spread) CB_CUDA(cudaStreamWaitEvent(s, gs.b_up[j], 0));
+                for (int s = 1; s < n; s++) {  // two streams, so that two copy engines and two links work at a time
+                    const int peer = (g + s) % n;
+                    CB_CUDA(cudaMemcpyPeerAsync(static_cast<char *>(comm->gpu[peer].buf[1]) + off, comm->gpu[peer].ordinal,
+                                                dB + off, gs.ordinal, bytes, gs.spread[s & 1]));
+                }
+            }
+            // b_spread[j]: this GPU's piece of block j is in its own memory and in every peer's
+            CB_CUDA(cudaEventRecord(gs.spread_join[j], gs.spread[0]));
+            CB_CUDA(cudaStreamWaitEvent(gs.spread[1], gs.spread_join[j], 0));
+            CB_CUDA(cudaEventRecord(gs.b_spread[j], gs.spread[1]));
+            return CUTE_B200_OK;
+        };
+        auto a_panel = [&](int i) -> cute_b200_status {
+            const int r0 = i * per, r = rows[g] - r0 < per ? rows[g] - r0 : per;
+            const size_t grow0 = size_t(begin[g]) + r0;
+            if (desc->k > 0)
+                CB_CUDA(cudaMemcpyAsync(dA + size_t(r0) * k_bytes, static_cast<const char *>(hA) + grow0 * k_bytes, size_t(r) * k_bytes,
+                                        cudaMemcpyHostToDevice, gs.up));
+            if (reads_c)  // the old values of these rows of C, all columns
+                CB_CUDA(cudaMemcpyAsync(dC + size_t(r0) * c_pitch, static_cast<const char *>(hC) + grow0 * c_pitch, size_t(r) * c_pitch,
+                                        cudaMemcpyHostToDevice, gs.up));
+            CB_CUDA(cudaEventRecord(gs.a_up[i], gs.up));
+            return CUTE_B200_OK;
+        };
+        auto phase2 = [&]() -> cute_b200_status {
+            if (panels > 0) CB_TRY(a_panel(0));
+            CB_TRY(b_piece(0));
+            for (int i = 1; i < panels; i++) CB_TRY(a_panel(i));
+            for (int j = 1; j < blocks; j++) CB_TRY(b_piece(j));
+            return CUTE_B200_OK;
+        };
         st = phase2();
 #ifdef CB_TRACE_SHARDED
-        cudaEventRecord(tr[1], gs.up);         // B share is up
-        cudaEventRecord(tr[2], gs.spread[1]);  // and with every peer
+        cudaEventRecord(tr[1], gs.up);  // everything is queued for the way up
+        cudaEventRecord(tr[2], gs.spread[1]);                // and every piece of B is with every peer
 #endif
         if (!comm->barrier.arrive(st == CUTE_B200_OK)) {
             cudaDeviceSynchronize();
             return st != CUTE_B200_OK ? st : fail(CUTE_B200_ERR_CUDA, "another GPU of the call failed");
         }
 
-        // phase 3: rows of A come up in panels; each panel is multiplied against all of B as soon as
-        // every share of B has landed here, and its rows of C go down while the next panel comes up
-        auto phase3 = [&]() -> cute_b200_status {
-            for (int peer = 0; peer < n; peer++) CB_CUDA(cudaStreamWaitEvent(gs.compute, comm->gpu[peer].b_spread, 0));
-            if (rows[g] == 0) return CUTE_B200_OK;
-            int panels = 8;
-            while (panels > 1 && (rows[g] / panels < 256 || size_t(rows[g] / panels) * c_pitch < (size_t(4) << 20))) panels /= 2;
-            const int per = ((rows[g] + panels - 1) / panels + 127) / 128 * 128;
-            int i = 0;
-            for (int r0 = 0; r0 < rows[g]; r0 += per, i++) {
-                const int r = rows[g] - r0 < per ? rows[g] - r0 : per;
-                const size_t grow0 = size_t(begin[g]) + r0;
-                if (desc->k > 0)
-                    CB_CUDA(cudaMemcpyAsync(dA + size_t(r0) * k_bytes, static_cast<const char *>(hA) + grow0 * k_bytes,
-                                            size_t(r) * k_bytes, cudaMemcpyHostToDevice, gs.up));
-                if (reads_c)
-                    CB_CUDA(cudaMemcpyAsync(dC + size_t(r0) * c_pitch, static_cast<const char *>(hC) + grow0 * c_pitch,
-                                            size_t(r) * c_pitch, cudaMemcpyHostToDevice, gs.up));
-                CB_CUDA(cudaEventRecord(gs.a_up[i], gs.up));
-                CB_CUDA(cudaStreamWaitEvent(gs.compute, gs.a_up[i], 0));
-                cute_b200_gemm_desc d = *desc;
-                d.m = r;
+        // phase 3 (every GPU has recorded its events by now): block (panel i, columns of block 0) as
+        // soon as panel i and all pieces of block 0 are here, then block j of all rows as soon as all
+        // pieces of block j are; each goes down behind its product.
+        auto product = [&](int r0, int r, int j) -> cute_b200_status {
+            const int c0 = col0[j], w = col0[j + 1] - c0;
+            char *c_at = dC + size_t(r0) * c_pitch + size_t(c0) * esize;
+            cute_b200_gemm_desc d = *desc;
+            d.m = r, d.n = w;
+            if (blocks == 1)  // all columns: a dense C, which may also split k (and takes k = 0)
                 CB_TRY(gemm_tn(d, reinterpret_cast<uint64_t>(dA + size_t(r0) * k_bytes), reinterpret_cast<uint64_t>(dB),
-                               reinterpret_cast<uint64_t>(dC + size_t(r0) * c_pitch), gs.compute, *dev));
-                CB_CUDA(cudaEventRecord(gs.c_done[i], gs.compute));
-                CB_CUDA(cudaStreamWaitEvent(gs.down, gs.c_done[i], 0));
+                               reinterpret_cast<uint64_t>(c_at), gs.compute, *dev));
+            else
+                CB_TRY(gemm_tn_strided(d, reinterpret_cast<uint64_t>(dA + size_t(r0) * k_bytes),
+                                       reinterpret_cast<uint64_t>(dB + size_t(c0) * k_bytes), reinterpret_cast<uint64_t>(c_at), desc->n,
+                                       gs.compute, *dev));
+            CB_CUDA(cudaEventRecord(gs.c_done, gs.compute));
+            CB_CUDA(cudaStreamWaitEvent(gs.down, gs.c_done, 0));
+            char *h_at = static_cast<char *>(hC) + (size_t(begin[g]) + r0) * c_pitch + size_t(c0) * esize;
+            if (blocks == 1)
+                CB_CUDA(cudaMemcpyAsync(h_at, c_at, size_t(r) * c_pitch, cudaMemcpyDeviceToHost, gs.down));
+            else
+                CB_CUDA(cudaMemcpy2DAsync(h_at, c_pitch, c_at, c_pitch, size_t(w) * esize, size_t(r), cudaMemcpyDeviceToHost, gs.down));
+            return CUTE_B200_OK;
+        };
+        auto phase3 = [&]() -> cute_b200_status {
+            if (rows[g] == 0) return CUTE_B200_OK;
+            for (int j = 0; j < blocks; j++) {
+                for (int peer = 0; peer < n; peer++) CB_CUDA(cudaStreamWaitEvent(gs.compute, comm->gpu[peer].b_spread[j], 0));
+                if (j > 0) {
+                    CB_TRY(product(0, rows[g], j));
+                    continue;
+                }
+                for (int i = 0; i < panels; i++) {
+                    CB_CUDA(cudaStreamWaitEvent(gs.compute, gs.a_up[i], 0));
+                    CB_TRY(product(i * per, rows[g] - i * per < per ? rows[g] - i * per : per, 0));
 #ifdef CB_TRACE_SHARDED
-                if (i == 0) cudaEventRecord(tr[3], gs.compute), cudaEventRecord(tr[4], gs.down);  // first product done, first way down begins
+                    if (i == 0) cudaEventRecord(tr[3], gs.compute), cudaEventRecord(tr[4], gs.down);  // first product done, first way down begins
 #endif
-                CB_CUDA(cudaMemcpyAsync(static_cast<char *>(hC) + grow0 * c_pitch, dC + size_t(r0) * c_pitch, size_t(r) * c_pitch,
-                                        cudaMemcpyDeviceToHost, gs.down));
+                }
             }
             return CUTE_B200_OK;
         };
@@ -478,18 +523,18 @@ cute_b200_status gemm_tn_sharded_host(void *p, const cute_b200_gemm_desc *desc, 
         cudaEventRecord(tr[6], gs.compute);
         cudaEventRecord(tr[7], gs.down);
 #endif
-        const cute_b200_status sync = sync_and_check();
+        const cute_b200_status sync = sync_and_check();  // everything queued reads or writes the caller's buffers
 #ifdef CB_TRACE_SHARDED
         {
             float ms[8] = {};
             for (int i = 1; i < 8; i++) cudaEventElapsedTime(&ms[i], tr[0], tr[i]);
             const double h0 = std::chrono::duration<double, std::milli>(host_p2 - t_start).count();
             const double h1 = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t_start).count();
-            fprintf(stderr, "trace gpu %d: host->phase2 %.2f | B up %.2f spread %.2f gemm0 %.2f d2h0-start %.2f A-up-all %.2f gemm-all %.2f d2h-all %.2f | host end %.2f ms\n",
+            fprintf(stderr, "trace gpu %d: host->phase2 %.2f | all up %.2f spread %.2f gemm0 %.2f d2h0-start %.2f up-end %.2f gemm-all %.2f d2h-all %.2f | host end %.2f ms\n",
                     g, h0, ms[1], ms[2], ms[3], ms[4], ms[5], ms[6], ms[7], h1);
             for (auto &e : tr) cudaEventDestroy(e);
         }
-#endif  // everything queued reads or writes the caller's buffers
+#endif
         // nobody's B may be overwritten by the next call while a slower GPU still multiplies: leave together
         comm->barrier.arrive(true);
         return st != CUTE_B200_OK ? st : sync;

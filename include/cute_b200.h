@@ -329,11 +329,14 @@ cute_b200_status cute_b200_wait_signal(uint64_t dSignals, uint32_t mask, uint32_
  * cute_b200_gemm_tn_sharded_host (host buffers, the convention of
  * CudaContext::launch): hA (m, k), hB (n, k) and hC (m, n) are whole matrices
  * in host memory (pinned memory makes the copies faster).  Every GPU uploads
- * its rows of A and only its 1/ngpus share of B's rows; the shares are passed
- * on to the other GPUs by device-to-device copies over NVLink while A's panels
- * come up; each panel of rows is multiplied as soon as B is complete and its
- * rows of C go back to hC while the next panel is on its way.  hC is read
- * first only when beta != 0.  Staging memory is kept by the communicator.
+ * its rows of A and only 1/ngpus of B's rows, and passes what it fetched of B
+ * on to the other GPUs by device-to-device copies over NVLink.  The way back
+ * to hC is the longest leg, so it starts early: from 8192 columns on, C is cut
+ * into blocks of about 4096 columns and B goes up block by block; the first
+ * block is multiplied panel by panel of A's rows as they arrive, the later
+ * ones as soon as their rows of B are complete, and every finished block of C
+ * goes back to hC while the following uploads and products run ahead.  hC is
+ * read first only when beta != 0.  Staging memory is kept by the communicator.
  * `seconds`, if not NULL, receives the duration of the call. */
 enum {
     CUTE_B200_REPLICATE_NONE = 0,

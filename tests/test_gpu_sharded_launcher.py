@@ -81,10 +81,14 @@ def test_sharded_gemm_on_device_buffers(lib, gpu, m, n, k, cdt_bf16):
 
 @pytest.mark.parametrize("m,n,k,cdt_bf16,alpha,beta", [(1024, 640, 256, True, 1.0, 0.0), (1000, 264, 136, False, 1.0, 0.0),
                                                        (100, 136, 64, False, 1.5, -0.5), (4096, 1024, 512, True, 1.0, 0.0),
-                                                       (300, 200, 0, False, 2.0, 0.5)])
+                                                       (300, 200, 0, False, 2.0, 0.5),
+                                                       # 8192 columns and more: C goes in blocks of columns, B up block by block
+                                                       (700, 8448, 128, True, 1.0, 0.0), (520, 8200, 72, False, 1.5, -0.5),
+                                                       (256, 16640, 64, True, 1.0, 0.0)])
 def test_sharded_gemm_on_host_buffers(lib, gpu, m, n, k, cdt_bf16, alpha, beta):
     """Whole matrices in host memory: every GPU uploads its rows of A and its share of B,
-    the shares are passed around, C comes back row block by row block."""
+    the shares are passed around, C comes back block by block (panels of rows, and from 8192 columns on
+    also blocks of columns)."""
     import torch
     rng = np.random.default_rng(m * 3 + n)
     a = oracle.f32_to_bf16_bits(rng.integers(-8, 9, (m, k)).astype(np.float32))
