@@ -437,9 +437,13 @@ def main():
         all_parity = [None] * world
         dist.all_gather_object(all_parity, parity, group=host_group)
         sums = torch.zeros(len(variants), device="cuda", dtype=torch.float64)
+        gate = torch.zeros(1, device="cuda")
         for r in range(reps + 1):
             for i, fn in enumerate(variants.values()):
                 barrier()
+                # the ranks' hosts leave the barrier at slightly different times; a tiny all-reduce queued in
+                # front of the step lets every rank's stream pass e0 at the same moment instead
+                dist.all_reduce(gate)
                 e0.record()
                 fn()
                 e1.record()
@@ -465,7 +469,8 @@ def main():
             "fused_register_stores": "one GEMM launch whose epilogue warps store every chunk to the peers' C from registers "
                                      "(32 bytes per lane), 128 rows of C per CTA; closing barrier",
         }
-        rep = {"unit": UNIT, "timing": "%d interleaved steps of each variant, CUDA events, max over ranks" % reps}
+        rep = {"unit": UNIT, "timing": "%d interleaved steps of each variant, CUDA events from a device-side rendezvous of the ranks "
+                                       "to the end of the step, max over ranks" % reps}
         # What bounds a step that leaves all of C on every GPU: the slower of this GPU's share of the flops at the
         # measured cuBLAS peak and the bytes it must send at the measured peer-copy rate (770 GB/s per direction).
         # The variants run back to back for about a second, so the GPU sits at its power cap: the sustained figure.
