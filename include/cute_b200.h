@@ -256,8 +256,11 @@ cute_b200_status cute_b200_copy_async(uint64_t dst, uint64_t src, uint64_t bytes
  * NVLink).  alpha must be 1 and beta 0; no k split; 1 <= count <= 8; every
  * destination aligned like the first (same offset within 32 bytes).  The
  * caller makes the result visible to the peers the usual way (stream
- * synchronisation followed by a barrier among the processes).  No counterpart
- * in the reference. */
+ * synchronisation followed by a barrier among the processes).  Measured: a
+ * destination exported by CUDA IPC should be an allocation whose size is a
+ * whole number of 2 MiB (2 GiB + 256 bytes in one allocation made the stores
+ * of eight GPUs into one another more than twice as slow as 2 GiB).  No
+ * counterpart in the reference. */
 cute_b200_status cute_b200_gemm_tn_multi(const cute_b200_gemm_desc *desc, uint64_t dA, uint64_t dB,
                                          const uint64_t *dC_list, int32_t count, void *stream);
 
