@@ -726,6 +726,10 @@ cute_b200_status cute_b200_alloc(uint64_t bytes, uint64_t *device_out) {
     if (!device_out) return fail(CUTE_B200_ERR_NULL_POINTER, "alloc: null output");
     DeviceState *dev;
     CB_TRY(current_device(&dev));
+    // Large buffers are made a whole number of 2 MiB: a 2 GiB + 256 byte allocation, exported by CUDA IPC,
+    // took the stores of peer GPUs at less than half the rate of a 2 GiB one (measured on eight B200s).
+    constexpr uint64_t kGranule = uint64_t(2) << 20;
+    if (bytes > kGranule) bytes = (bytes + kGranule - 1) / kGranule * kGranule;
     void *p = nullptr;
     CB_CUDA(cudaMalloc(&p, bytes ? bytes : 1));
     *device_out = reinterpret_cast<uint64_t>(p);

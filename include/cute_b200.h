@@ -236,8 +236,10 @@ cute_b200_status cute_b200_gemm_tn_shard(const cute_b200_gemm_desc *desc, int32_
  * cute_b200_alloc, exports it, and opens the others' handles (CUDA IPC; the
  * 64-byte handles travel over whatever channel the caller has, e.g. the
  * torch.distributed store).  cute_b200_copy_async is a device-to-device copy
- * on a stream (copy engines, no SM), local or to a peer mapping.  No
- * counterpart in the reference (single GPU). */
+ * on a stream (copy engines, no SM), local or to a peer mapping.
+ * cute_b200_alloc makes every buffer above 2 MiB a whole number of 2 MiB
+ * (see cute_b200_gemm_tn_multi for why).  No counterpart in the reference
+ * (single GPU). */
 cute_b200_status cute_b200_alloc(uint64_t bytes, uint64_t *device_out);
 cute_b200_status cute_b200_ipc_export(uint64_t device, uint8_t handle_out[64]);
 cute_b200_status cute_b200_ipc_open(const uint8_t handle[64], uint64_t *device_out);
