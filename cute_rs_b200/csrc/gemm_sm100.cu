@@ -380,6 +380,10 @@ __global__ void __launch_bounds__(num_threads(BN, MH), 1)
     }
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // First pass of a split GEMM: the kernel that adds the planes is queued behind this one as a
+    // programmatic dependent, so that its launch and scheduling overlap this kernel; it waits
+    // for this grid's completion itself before it reads a plane.
+    if (p.splits > 1 && threadIdx.x == 0) ptx::griddep_launch_dependents();
 
     if (warp == 0) {
         // ------------------------------------------------------------ producer
@@ -789,6 +793,7 @@ __global__ void gemm_k0_kernel(void *C, size_t count, float alpha, float beta) {
 template <bool C_BF16>
 __global__ void __launch_bounds__(256) gemm_splitk_reduce(const float *__restrict__ partial, int splits, size_t plane,
                                                           size_t count, void *C, float alpha, float beta) {
+    ptx::griddep_wait();  // launched as a programmatic dependent of the first pass: wait for its planes
     const size_t i4 = (size_t(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
     if (i4 >= count) return;
     const bool plain = (alpha == 1.0f && beta == 0.0f);
@@ -1019,7 +1024,7 @@ double choose_tiling(int m, int n, int k, int c_bytes, int sm_count, int want_gr
                     }
                     double t = waves * (unit_time + unit_latency);
                     if (g == 2) t += pair_start;
-                    if (s > 1) t += (double(s + 1) * m * n * 4 + double(m) * n * c_bytes) / hbm + 6e-6;  // + the second launch
+                    if (s > 1) t += (double(s + 1) * m * n * 4 + double(m) * n * c_bytes) / hbm + 3.5e-6;  // + the second launch (a programmatic dependent: about half of a plain launch)
                     if (t < best) {
                         best = t;
                         *group = g, *bn = b, *mh = h, *splits = s;
@@ -1390,14 +1395,20 @@ static cute_b200_status gemm_tn_ex(const cute_b200_gemm_desc &d, uint64_t a, uin
         CB_GEMM_VARIANTS(CB_CASE)
 #undef CB_CASE
         CB_TRY(st);
-        const unsigned blocks = unsigned((plane + 1023) / 1024);
-        if (c_bf16)
-            gemm_splitk_reduce<true><<<blocks, 256, 0, stream>>>(static_cast<const float *>(scratch), splits, plane, plane,
-                                                                 p.C, d.alpha, d.beta);
-        else
-            gemm_splitk_reduce<false><<<blocks, 256, 0, stream>>>(static_cast<const float *>(scratch), splits, plane, plane,
-                                                                  p.C, d.alpha, d.beta);
-        CB_CUDA(cudaGetLastError());
+        // The second pass is a programmatic dependent of the first: it is scheduled while the first still
+        // runs and waits (griddepcontrol.wait) for the planes, which hides its launch behind the first pass.
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(unsigned((plane + 1023) / 1024));
+        cfg.blockDim = dim3(256);
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = (d.tuning[0] & 32) ? 0 : 1;  // bit 5: plain stream order (measurements)
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        const float *planes = static_cast<const float *>(scratch);
+        if (c_bf16) CB_CUDA(cudaLaunchKernelEx(&cfg, gemm_splitk_reduce<true>, planes, splits, plane, plane, p.C, d.alpha, d.beta));
+        else CB_CUDA(cudaLaunchKernelEx(&cfg, gemm_splitk_reduce<false>, planes, splits, plane, plane, p.C, d.alpha, d.beta));
         count_launch();
         return scratch_release(stream);
     }

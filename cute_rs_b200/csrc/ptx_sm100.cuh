@@ -209,6 +209,13 @@ __device__ __forceinline__ void tmem_ld_wait(uint32_t (&v)[32]) {
 
 // Wait for all of this thread's tcgen05.ld reads; every array that was loaded then goes through
 // pin(), so that the compiler cannot schedule a use of its registers above the wait.
+// Programmatic dependent launch.  launch_dependents: a kernel queued behind this one with the
+// programmatic-serialisation attribute may be scheduled once every CTA of this grid has said so
+// (or has exited); griddep_wait, in that kernel, returns when this grid has completed and its
+// memory operations are visible.  Both are no-ops in a launch without such a dependence.
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ void tmem_ld_wait_all() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void pin(uint32_t (&v)[32]) {
     asm volatile(""
