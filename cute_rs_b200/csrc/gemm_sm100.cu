@@ -380,10 +380,14 @@ __global__ void __launch_bounds__(num_threads(BN, MH), 1)
     }
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    // First pass of a split GEMM: the kernel that adds the planes is queued behind this one as a
-    // programmatic dependent, so that its launch and scheduling overlap this kernel; it waits
-    // for this grid's completion itself before it reads a plane.
-    if (p.splits > 1 && threadIdx.x == 0) ptx::griddep_launch_dependents();
+    // Programmatic dependent launch, both ways.  This kernel may have been scheduled while the kernel
+    // before it in the stream was still running (only another launch of this library lets that happen):
+    // everything so far touched only this CTA's shared memory and TMEM; nothing below may read or write
+    // global memory before that kernel has completed.  And whatever is queued behind this kernel as a
+    // programmatic dependent (the kernel that adds the planes of a split GEMM, or the next GEMM) may be
+    // scheduled from now on; it waits the same way.
+    ptx::griddep_wait();
+    if (threadIdx.x == 0) ptx::griddep_launch_dependents();
 
     if (warp == 0) {
         // ------------------------------------------------------------ producer
@@ -925,13 +929,17 @@ cute_b200_status launch(const CUtensorMap &tmA, const CUtensorMap &tmB, const CM
     cfg.blockDim = dim3(num_threads(BN, MH));
     cfg.dynamicSmemBytes = C::SMEM_BYTES;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = CTA_GROUP;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    // Queued behind another launch of this library, the kernel is set up (barriers, TMEM) while that one
+    // drains; its griddepcontrol.wait keeps every global access behind the predecessor's completion.
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = (p.debug & 32) ? 0 : 1;  // bit 5: plain stream order (measurements)
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 2;
     CB_CUDA(cudaLaunchKernelEx(&cfg, gemm_tn_kernel<CTA_GROUP, BN, MH, C_BF16>, tmA, tmB, tmC, p));
     count_launch();
     return CUTE_B200_OK;

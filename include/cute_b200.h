@@ -102,8 +102,8 @@ typedef struct {
     int32_t tuning[2]; /* zero.  Measurement and test knobs: [0] bit 0 skips the loads, bit 1 the stores (results
                           are then meaningless), bits 2+3 make every in-kernel wait run out after 20 ms so that
                           the bounded-wait report can be tested, bit 4 makes cute_b200_gemm_tn_multi store to its
-                          destinations from registers instead of by TMA, bit 5 queues the second kernel of a split
-                          GEMM in plain stream order instead of as a programmatic dependent of the first;
+                          destinations from registers instead of by TMA, bit 5 queues the GEMM's kernels in plain
+                          stream order instead of as programmatic dependents of the kernel before them;
                           [1] row tiles walked per column step */
 } cute_b200_gemm_desc;
 
