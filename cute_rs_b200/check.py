@@ -462,6 +462,47 @@ def check_signal(seeds=range(6), **kw) -> None:
         run(programs, barriers, seed=seed, max_burst=2)
 
 
+def cluster_sum_schedule(kc: int = 2, warps: int = 8, mutations=()):
+    """The k split that is summed inside a cluster (GemmParams::kc): each of the kc CTAs holds the partial
+    sums of its k range; every epilogue warp writes its part of them to its CTA's shared memory, all
+    threads of the cluster meet at a cluster barrier, every warp then reads its rows from every CTA's
+    shared memory and stores them to C, and a second cluster barrier in the teardown keeps each CTA's
+    shared memory alive until all have read it (the final write below stands for its release).
+    Mutations:
+      "sum_before_barrier"     a warp reads the other CTAs' partial sums without the first cluster barrier
+      "barrier_of_one_cta"     the first barrier counts only the warps of the own CTA
+      "exit_without_barrier"   a CTA releases its shared memory without the second cluster barrier
+      "a_warp_skips_barrier"   one warp never arrives (what the bounded waits' fall-through prevents): deadlock
+    """
+    mut = set(mutations)
+    programs, barriers = {}, {}
+    total = kc * warps
+    for c in range(kc):
+        for w in range(warps):
+            prog = programs[f"epi{c}.{w}"] = []
+            prog.append(("st", f"part{c}.{w}"))                                  # TMEM -> this CTA's shared memory
+            if not ("a_warp_skips_barrier" in mut and (c, w) == (kc - 1, warps - 1)):
+                prog.append(("signal", "exchange"))
+            if "sum_before_barrier" not in mut:
+                prog.append(("wait_count", "exchange", warps if "barrier_of_one_cta" in mut else total))
+            for c2 in range(kc):                                                 # its rows of every CTA's partial sums
+                for w2 in range(warps):
+                    prog.append(("ld", f"part{c2}.{w2}"))
+            prog.append(("st", f"c.{c}.{w}"))
+            prog.append(("signal", "teardown"))
+            if "exit_without_barrier" not in mut:
+                prog.append(("wait_count", "teardown", total))
+            prog.append(("st", f"part{c}.{w}"))                                  # the CTA exits: its shared memory is reused
+    return programs, barriers
+
+
+def check_cluster_sum(seeds=range(6), **kw) -> None:
+    programs, barriers = cluster_sum_schedule(**kw)
+    for seed in seeds:
+        run(programs, barriers, seed=seed)
+        run(programs, barriers, seed=seed, max_burst=2)
+
+
 def tiling_from_library(info, cta_group: int) -> dict:
     """gemm_schedule's arguments for a tiling as the compiled kernel has it: `info`
     is the cute_b200_gemm_layout the library reports (ring depth, stage bytes,

@@ -126,6 +126,10 @@ struct Cfg {
     static constexpr uint32_t FULL_ARRIVALS = 1, EMPTY_ARRIVALS = 1, TFULL_ARRIVALS = 1;
     static constexpr uint32_t TEMPTY_ARRIVALS = 4 * epilogue_groups(BN, MH) * CTA_GROUP;
     static constexpr uint32_t EXPECT_TX_PER_KB = CTA_GROUP * KB_BYTES;  // bytes the (leader's) full barrier counts per k block of a stage
+    // Row pitch of a CTA's partial sums in shared memory when a cluster adds its k ranges (GemmParams::kc):
+    // 16 bytes more than a row of BN floats, so that the 32 lanes' 16-byte stores of a column group spread over the banks.
+    static constexpr uint32_t KC_PITCH = BN * 4 + 16;
+    static_assert(uint32_t(BM) * KC_PITCH <= STAGES * STAGE_BYTES, "the partial sums reuse the ring");
     static_assert(STAGES >= 2 && STAGES <= MAX_STAGES, "ring depth");
     static_assert(ACC_COLS * ACC_BUFS <= 512, "accumulators exceed TMEM");
     static_assert(SMEM_BYTES <= 227 * 1024, "shared memory");
@@ -150,6 +154,10 @@ struct GemmParams {
                    // producer issue nothing at all (every consumer wait then runs out), bit 3 shortens the limit
     int splits;              // k is cut into this many ranges, one work unit each (1 = no split)
     size_t split_stride;     // bytes between the partial-sum planes of consecutive ranges
+    // kc > 1 (single-CTA 128-row tiles only): the `splits` = kc ranges of a tile are computed by the kc CTAs
+    // of one cluster, which then add their partial sums through each other's shared memory and write C
+    // themselves - no planes in global memory, no second kernel.  One unit per CTA: the grid is tiles x kc.
+    int kc;
     uint32_t *status;
     // Further copies of C that receive the same result (other GPUs' C over NVLink peer mappings).
     // Plain epilogue, no k split.  push = 1: the pusher warp copies every finished tile from C to
@@ -344,9 +352,15 @@ __global__ void __launch_bounds__(num_threads(BN, MH), 1)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = CTA_GROUP == 1 ? 0u : ptx::cluster_ctarank();
-    const int cluster_id = blockIdx.x / CTA_GROUP;
-    const int num_clusters = gridDim.x / CTA_GROUP;
+    bool kc_mode = false;
+    if constexpr (CTA_GROUP == 1 && MH == 1) kc_mode = p.kc > 1;
+    const uint32_t kc_rank = kc_mode ? ptx::cluster_ctarank() : 0u;
+    const int cluster_id = kc_mode ? int(blockIdx.x) / p.kc : int(blockIdx.x) / CTA_GROUP;
+    const int num_clusters = kc_mode ? int(gridDim.x) / p.kc : int(gridDim.x) / CTA_GROUP;
     const int num_units = p.m_tiles * p.n_tiles * p.splits;
+    // Units of this CTA: first, first + step, ...  (With kc the cluster's CTAs take the kc ranges of one tile.)
+    const int unit_first = kc_mode ? cluster_id * p.kc + int(kc_rank) : cluster_id;
+    const int unit_step = kc_mode ? num_clusters * p.kc : num_clusters;
     const int k_blocks = (p.K + BK - 1) / BK;
     constexpr int nstages = C::STAGES;
     const uint64_t wait_limit = (p.debug & 8) ? 20ull * 1000 * 1000 : WAIT_LIMIT_NS;
@@ -398,7 +412,7 @@ __global__ void __launch_bounds__(num_threads(BN, MH), 1)
             uint32_t ph = 0;
             uint32_t filled = 0, filled_parity = 0;  // per stage: was it filled, and in which phase
             bool ok = true;
-            for (int t = cluster_id; t < num_units && ok && !(p.debug & 4); t += num_clusters) {
+            for (int t = unit_first; t < num_units && ok && !(p.debug & 4); t += unit_step) {
                 const Unit u = unit_of(t, p, k_blocks);
                 const TileCoord tc = tile_coord(u.tile, p);
                 const int row_a = (tc.tm * CTA_GROUP + int(rank)) * C::A_ROWS;
@@ -461,7 +475,7 @@ __global__ void __launch_bounds__(num_threads(BN, MH), 1)
             uint32_t ph = 0;
             bool ok = true, issued = false;
             int it = 0;
-            for (int t = cluster_id; t < num_units && ok; t += num_clusters) {
+            for (int t = unit_first; t < num_units && ok; t += unit_step) {
                 const Unit u = unit_of(t, p, k_blocks);
                 if (u.kb0 >= u.kb1) continue;  // an empty k range uses no accumulator
                 const int buf = it % C::ACC_BUFS;
@@ -542,7 +556,7 @@ __global__ void __launch_bounds__(num_threads(BN, MH), 1)
         bool ok = true;
         int it = 0;
         uint32_t tiles_done = 0;
-        for (int t = cluster_id; t < num_units && ok; t += num_clusters) {
+        for (int t = unit_first; t < num_units && ok; t += unit_step) {
             const Unit u = unit_of(t, p, k_blocks);
             const TileCoord tc = tile_coord(u.tile, p);
             const bool have_acc = u.kb0 < u.kb1;  // else this range contributes zeros
@@ -561,6 +575,29 @@ __global__ void __launch_bounds__(num_threads(BN, MH), 1)
             const int col_base = tc.tn * BN + (C::HALF ? int(q >> 1) * C::HALF_COLS : 0);
             const uint32_t taddr0 = tmem_base + ((q * 32u) << 16) + uint32_t(buf * C::ACC_COLS);
             auto col_of = [&](int i) { return ((i % CH) * EG + e) * 32; };  // within the accumulator's columns
+            if constexpr (CTA_GROUP == 1 && MH == 1) {
+                if (kc_mode) {
+                    // This CTA's partial sums go to its shared memory (the ring is idle: the CTA's only unit
+                    // has been multiplied), row r of the tile at r * KC_PITCH; the cluster adds them below.
+                    ptx::fence_proxy_async_shared();
+                    const uint32_t row_addr = ring + (q * 32u + uint32_t(lane)) * C::KC_PITCH;
+#pragma unroll 1
+                    for (int i = 0; i < ITEMS; i++) {
+                        uint32_t v[32];
+                        if (have_acc) {
+                            ptx::tmem_ld_32x32(taddr0 + uint32_t(col_of(i)), v);
+                            ptx::tmem_ld_wait(v);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; j++) v[j] = 0u;
+                        }
+#pragma unroll
+                        for (int g = 0; g < 8; g++)
+                            ptx::st_shared_v4(row_addr + uint32_t(col_of(i) + 4 * g) * 4u, v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+                    }
+                    continue;
+                }
+            }
             auto load = [&](int i, uint32_t(&v)[32]) {
                 if (have_acc) {
                     ptx::tmem_ld_32x32(taddr0 + uint32_t((i / CH) * C::HALF_COLS + col_of(i)), v);
@@ -723,10 +760,81 @@ __global__ void __launch_bounds__(num_threads(BN, MH), 1)
         __syncwarp();
     }
 
+    // ------------------------------------------- sum of the k ranges inside a cluster
+    if constexpr (CTA_GROUP == 1 && MH == 1) {
+        if (kc_mode) {
+            ptx::cluster_arrive();  // every CTA of the cluster has its partial sums in shared memory (or has given up)
+            ptx::cluster_wait();
+            if (warp >= 2 && warp < 2 + 4 * EG && unit_first < num_units && !*abort_flag) {
+                // CTA r of the cluster finishes rows [r, r + 1) * 128 / kc of the tile: a warp per row, a lane per
+                // four columns, the ranges added in ascending order (as the second kernel of the two-pass form does).
+                const TileCoord tc = tile_coord(unit_of(unit_first, p, k_blocks).tile, p);
+                const int rows_per = BM / p.kc;
+                const bool plain = (p.alpha == 1.0f && p.beta == 0.0f);
+                for (int r = warp - 2; r < rows_per; r += 4 * EG) {
+                    const int trow = int(kc_rank) * rows_per + r;
+                    const int grow = tc.tm * BM + trow;
+                    if (grow >= p.M) continue;
+#pragma unroll
+                    for (int seg = 0; seg < BN / 128; seg++) {
+                        const int tcol = seg * 128 + 4 * lane;
+                        const int gcol = tc.tn * BN + tcol;
+                        if (gcol >= p.N) continue;
+                        const uint32_t local = ring + uint32_t(trow) * C::KC_PITCH + uint32_t(tcol) * 4u;
+                        float4 acc = ptx::ld_shared_cluster_v4(ptx::mapa(local, 0));
+                        for (int c = 1; c < p.kc; c++) {
+                            const float4 b = ptx::ld_shared_cluster_v4(ptx::mapa(local, uint32_t(c)));
+                            acc.x = __fadd_rn(acc.x, b.x);
+                            acc.y = __fadd_rn(acc.y, b.y);
+                            acc.z = __fadd_rn(acc.z, b.z);
+                            acc.w = __fadd_rn(acc.w, b.w);
+                        }
+                        const float a4[4] = {acc.x, acc.y, acc.z, acc.w};
+                        auto epi = [&](float a, float c_old) { return __fadd_rn(__fmul_rn(p.alpha, a), __fmul_rn(p.beta, c_old)); };
+                        if constexpr (C_BF16) {
+                            __nv_bfloat16 *c = reinterpret_cast<__nv_bfloat16 *>(p.C) + size_t(grow) * p.ldc + gcol;
+                            if (p.c_vec_ok && gcol + 4 <= p.N) {
+                                float f[4];
+                                if (plain) {
+#pragma unroll
+                                    for (int j = 0; j < 4; j++) f[j] = a4[j];
+                                } else {
+                                    const uint2 old = *reinterpret_cast<const uint2 *>(c);
+                                    f[0] = epi(a4[0], __uint_as_float(old.x << 16));
+                                    f[1] = epi(a4[1], __uint_as_float(old.x & 0xffff0000u));
+                                    f[2] = epi(a4[2], __uint_as_float(old.y << 16));
+                                    f[3] = epi(a4[3], __uint_as_float(old.y & 0xffff0000u));
+                                }
+                                const __nv_bfloat162 h0 = __floats2bfloat162_rn(f[0], f[1]), h1 = __floats2bfloat162_rn(f[2], f[3]);
+                                *reinterpret_cast<uint2 *>(c) = make_uint2(*reinterpret_cast<const uint32_t *>(&h0), *reinterpret_cast<const uint32_t *>(&h1));
+                            } else {
+                                for (int j = 0; j < 4 && gcol + j < p.N; j++)
+                                    c[j] = __float2bfloat16_rn(plain ? a4[j] : epi(a4[j], __bfloat162float(c[j])));
+                            }
+                        } else {
+                            float *c = reinterpret_cast<float *>(p.C) + size_t(grow) * p.ldc + gcol;
+                            if (p.c_vec_ok && gcol + 4 <= p.N) {
+                                float4 o = acc;
+                                if (!plain) {
+                                    const float4 old = *reinterpret_cast<const float4 *>(c);
+                                    o = make_float4(epi(acc.x, old.x), epi(acc.y, old.y), epi(acc.z, old.z), epi(acc.w, old.w));
+                                }
+                                *reinterpret_cast<float4 *>(c) = o;
+                            } else {
+                                for (int j = 0; j < 4 && gcol + j < p.N; j++) c[j] = plain ? a4[j] : epi(a4[j], c[j]);
+                            }
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+        }
+    }
+
     // ---------------------------------------------------------------- teardown
     ptx::tc_fence_before();
     __syncthreads();
-    if constexpr (CTA_GROUP == 2) {  // the peer may still arrive on our barriers or read our tiles
+    if (CTA_GROUP == 2 || kc_mode) {  // the peer may still arrive on our barriers or read our shared memory
         ptx::cluster_arrive();
         ptx::cluster_wait();
     }
@@ -916,6 +1024,11 @@ cute_b200_status launch(const CUtensorMap &tmA, const CUtensorMap &tmB, const CM
     const long long tiles = (long long)p.m_tiles * p.n_tiles * p.splits;
     int clusters = sm_count / CTA_GROUP;
     if (tiles < clusters) clusters = int(tiles);
+    const bool kc = CTA_GROUP == 1 && MH == 1 && p.kc > 1;
+    if (kc) {  // one unit per CTA, the kc ranges of a tile in one cluster
+        if (tiles > (1 << 20)) return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "gemm_tn: too many tiles for the in-cluster k split");
+        clusters = int(tiles);
+    }
     // Walk about sqrt(#concurrent tiles) row tiles before moving to the next
     // column so that a wave of CTAs covers a near-square patch of C.
     int gm = 1;
@@ -931,7 +1044,7 @@ cute_b200_status launch(const CUtensorMap &tmA, const CUtensorMap &tmB, const CM
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = CTA_GROUP;
+    attr[0].val.clusterDim.x = kc ? unsigned(p.kc) : unsigned(CTA_GROUP);
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     // Queued behind another launch of this library, the kernel is set up (barriers, TMEM) while that one
@@ -967,7 +1080,7 @@ double tiling_efficiency(int group, int bn, int mh) {
     // The 64-row pair tile is bound by the rate at which one thread can issue cta_group::2 MMAs
     // (about 115 clocks each, whatever their size): 8192 x 128 x 8192 runs 0.23 us per k block,
     // 8192 x 256 x 8192 0.31 us.
-    if (mh == 0) return bn == 128 ? 0.45 : 0.67;
+    if (mh == 0) return bn == 128 ? 0.40 : 0.67;
     double e = 1.0;
     if (group == 1) e *= (mh == 2 ? 0.96 : 0.86);
     else if (mh == 1) e *= 0.92;
@@ -988,8 +1101,16 @@ double tiling_efficiency(int group, int bn, int mh) {
 // split above min_splits must leave each range at least four k blocks.
 // *mh receives the 128-row accumulators per CTA, 0 for the 64-row pair tile.
 // Returns the estimate in seconds.
+// Whether a k split is summed inside the kernel by the CTAs of a cluster (GemmParams::kc): single-CTA
+// 128-row tiles, two or four ranges, all units in one wave.
+bool kc_applies(int m, int n, int g, int b, int h, int s, int sm_count) {
+    if (g != 1 || h != 1 || (s != 2 && s != 4)) return false;
+    const long long units = (long long)((m + BM - 1) / BM) * ((n + b - 1) / b) * s;
+    return units <= sm_count;
+}
+
 double choose_tiling(int m, int n, int k, int c_bytes, int sm_count, int want_group, int want_bn, int want_rows,
-                     int want_splits, int min_splits, int max_splits, int *group, int *bn, int *mh, int *splits) {
+                     int want_splits, int min_splits, int max_splits, bool allow_kc, int *group, int *bn, int *mh, int *splits) {
     const double sm_rate = 1.0e13;       // dense 16-bit flop/s of one SM at the clocks a GEMM sustains
     const double unit_latency = 2.5e-6;  // fill the ring, drain the accumulator
     // A launch of CTA pairs starts about 2 us later than one of single CTAs (cluster scheduling and the
@@ -1032,7 +1153,10 @@ double choose_tiling(int m, int n, int k, int c_bytes, int sm_count, int want_gr
                     }
                     double t = waves * (unit_time + unit_latency);
                     if (g == 2) t += pair_start;
-                    if (s > 1) t += (double(s + 1) * m * n * 4 + double(m) * n * c_bytes) / hbm + 3.5e-6;  // + the second launch (a programmatic dependent: about half of a plain launch)
+                    if (s > 1) {
+                        if (allow_kc && kc_applies(m, n, g, b, h, s, sm_count)) t += 3.0e-6;  // the exchange through shared memory
+                        else t += (double(s + 1) * m * n * 4 + double(m) * n * c_bytes) / hbm + 3.5e-6;  // planes + the second launch (a programmatic dependent)
+                    }
                     if (t < best) {
                         best = t;
                         *group = g, *bn = b, *mh = h, *splits = s;
@@ -1174,7 +1298,7 @@ cute_b200_status gemm_tn_static(const cute_b200_gemm_desc &d, uint64_t a, uint64
     // two ranges and at most what the built-in array (and k) allow.
     int group = 2, bn = 256, mh = 2, splits = 2;
     choose_tiling(d.m, d.n, d.k, c_bf16 ? 2 : 4, setup->sm_count, d.cta_group, d.tile_n, d.tile_m, d.split_k, 2,
-                  int(max_splits_by_scratch < 16 ? max_splits_by_scratch : 16), &group, &bn, &mh, &splits);
+                  int(max_splits_by_scratch < 16 ? max_splits_by_scratch : 16), false, &group, &bn, &mh, &splits);
 
     GemmParams p = {};
     p.C = setup->scratch;
@@ -1339,7 +1463,9 @@ static cute_b200_status gemm_tn_ex(const cute_b200_gemm_desc &d, uint64_t a, uin
     if (d.split_k < 0 || d.split_k > 16)
         return fail(CUTE_B200_ERR_INVALID_ARGUMENT, "gemm_tn: split_k must be 0 (choose) to 16, got %d", d.split_k);
     int group = 2, bn = 256, mh = 2, splits = 1;
-    choose_tiling(d.m, d.n, d.k, c_bf16 ? 2 : 4, dev.sm_count, d.cta_group, d.tile_n, d.tile_m, d.split_k, 1, 16,
+    // tuning[0] bit 7 keeps a k split in its two-kernel form (measurements, and the test that the two forms agree)
+    const bool allow_kc = ex.extra_count == 0 && !(d.tuning[0] & 128);
+    choose_tiling(d.m, d.n, d.k, c_bf16 ? 2 : 4, dev.sm_count, d.cta_group, d.tile_n, d.tile_m, d.split_k, 1, 16, allow_kc,
                   &group, &bn, &mh, &splits);
 
     GemmParams p = {};
@@ -1384,6 +1510,15 @@ static cute_b200_status gemm_tn_ex(const cute_b200_gemm_desc &d, uint64_t a, uin
         p.push = 1;
     }
 
+    // A split in two or four of single-CTA 128-row tiles can be summed inside the kernel: the CTAs of a
+    // cluster take a tile's k ranges and add their partial sums through shared memory.
+    if (allow_kc && kc_applies(d.m, d.n, group, bn, mh, splits, dev.sm_count)) {
+        p.kc = splits;
+#define CB_CASE(G, N_, H, BF) \
+    if (G == 1 && H == 1 && bn == N_ && c_bf16 == BF) return launch<G, N_, H, BF>(tmA, tmB, tmC, p, dev.sm_count, stream);
+        CB_GEMM_VARIANTS(CB_CASE)
+#undef CB_CASE
+    }
     if (splits > 1) {
         // First pass: every k range writes an f32 plane of partial sums into the
         // library's scratch buffer; second pass adds the planes and applies the
@@ -1432,7 +1567,7 @@ cute_b200_status gemm_plan(const cute_b200_gemm_desc &d, int sm_count, int32_t o
     if (sm_count <= 0) sm_count = 148;
     int group = 2, bn = 256, mh = 2, splits = 1;
     choose_tiling(d.m, d.n, d.k, d.c_dtype == CUTE_B200_BF16 ? 2 : 4, sm_count, d.cta_group, d.tile_n, d.tile_m, d.split_k, 1, 16,
-                  &group, &bn, &mh, &splits);
+                  !(d.tuning[0] & 128), &group, &bn, &mh, &splits);
     out[0] = group, out[1] = bn, out[2] = mh == 0 ? 64 : 128 * mh, out[3] = splits;
     return CUTE_B200_OK;
 }

@@ -93,8 +93,11 @@ typedef struct {
     int32_t cta_group; /* 0 = choose; 1 = one CTA per tile; 2 = a CTA pair shares each tile's MMAs */
     int32_t tile_m;    /* rows of C per CTA: 0 = choose; 128 or 256; 64 = the pair tile for few row tiles and a long
                           k (needs cta_group 0 or 2): 16 KiB stages, a 12-deep ring */
-    int32_t split_k;   /* k ranges computed as separate work units and summed in ascending order by a second kernel
-                          through an f32 scratch buffer the library allocates on first need: 0 = choose, 1 = never,
+    int32_t split_k;   /* k ranges computed as separate work units and summed in ascending order, either inside the
+                          kernel (single-CTA 128-row tiles cut in two or four ranges that fit one wave: the CTAs of a
+                          cluster take a tile's ranges and add their partial sums through shared memory) or by a second
+                          kernel through an f32 scratch buffer the library allocates on first need - the same sums in
+                          the same order, hence the same bits: 0 = choose, 1 = never,
                           2..16 = exactly that many (cut down to the number of 64-wide k blocks when k is shorter;
                           ranges left without a block contribute zeros).  The scratch is one buffer per device shared
                           by all streams: the library orders split launches on different streams one behind the
@@ -103,7 +106,8 @@ typedef struct {
                           are then meaningless), bits 2+3 make every in-kernel wait run out after 20 ms so that
                           the bounded-wait report can be tested, bit 4 makes cute_b200_gemm_tn_multi store to its
                           destinations from registers instead of by TMA, bit 5 queues the GEMM's kernels in plain
-                          stream order instead of as programmatic dependents of the kernel before them;
+                          stream order instead of as programmatic dependents of the kernel before them,
+                          bit 7 keeps every k split in its two-kernel form;
                           [1] row tiles walked per column step */
 } cute_b200_gemm_desc;
 

@@ -425,7 +425,8 @@ def test_gemm_alpha_beta_epilogue(lib, gpu, cdt_name, alpha, beta, tile_m):
 @pytest.mark.parametrize("split_k", [2, 3, 5, 6, 16])
 @pytest.mark.parametrize("cdt_name,alpha,beta", [("f32", 1.0, 0.0), ("bf16", 1.0, 0.0), ("f32", 1.5, -0.5), ("bf16", 2.0, 1.0)])
 def test_gemm_split_k(lib, gpu, m, n, k, split_k, cdt_name, alpha, beta):
-    """k cut into ranges summed by the second kernel: exact on integer data.  The
+    """k cut into ranges summed by the second kernel (or, where the chosen tiling is a single-CTA
+    128-row tile cut in two in one wave, inside the kernel by a cluster): exact on integer data.  The
     library takes the asked number of ranges as it is, cut down to the number of
     64-wide k blocks (k = 64 therefore runs unsplit); where the blocks do not
     divide evenly the last ranges stay empty and contribute zeros (k = 1600 in 6
@@ -438,6 +439,41 @@ def test_gemm_split_k(lib, gpu, m, n, k, split_k, cdt_name, alpha, beta):
     got = run_gemm(lib, a_bits, b_bits, lib.F16, cdt, alpha, beta, c0=c0, split_k=split_k)
     want = oracle.gemm_tn(a_bits, b_bits, lib.F16, cdt, alpha, beta, c_init=c0)
     assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("m,n,k,tile_n,split_k", [(128, 128, 256, 128, 2), (256, 128, 512, 128, 2), (1000, 200, 1024, 128, 4),
+                                                  (384, 256, 512, 256, 2), (300, 520, 2048, 256, 4), (128, 136, 192, 128, 2),
+                                                  (143, 365, 1080, 0, 2), (520, 264, 4160, 0, 4), (9, 7, 512, 128, 4)])
+@pytest.mark.parametrize("cdt_name,alpha,beta", [("f32", 1.0, 0.0), ("bf16", 1.0, 0.0), ("f32", 1.5, -0.5), ("bf16", 2.0, 1.0)])
+def test_gemm_split_k_summed_in_the_cluster(lib, gpu, m, n, k, tile_n, split_k, cdt_name, alpha, beta):
+    """Single-CTA 128-row tiles cut in two or four ranges that fit one wave: the CTAs of a cluster
+    take a tile's ranges, add their partial sums through each other's shared memory (ascending, like
+    the second kernel of the two-pass form) and write C - one launch.  Exact on integer data; and on
+    random data the same bits as the two-pass form (tuning bit 7), whose sums it restates."""
+    import torch
+    cdt = lib.F32 if cdt_name == "f32" else lib.BF16
+    a, b, c = lcg_buffers([m * k, n * k, m * n], small=True)
+    a_bits, b_bits = oracle.f32_to_bf16_bits(a.reshape(m, k)), oracle.f32_to_bf16_bits(b.reshape(n, k))
+    c0 = c.reshape(m, n) if cdt == lib.F32 else oracle.f32_to_bf16_bits(c.reshape(m, n))
+    want = oracle.gemm_tn(a_bits, b_bits, oracle.BF16, cdt, alpha, beta, c_init=c0)
+
+    def run(a_bits, b_bits, tuning):
+        dA, dB, dC = dev(a_bits), dev(b_bits), dev(c0)
+        desc = lib.gemm_desc(m, n, k, lib.BF16, cdt, alpha, beta, tile_n, 1, 128, split_k)
+        desc.tuning[0] = tuning
+        before = lib.launch_count()
+        lib.gemm_tn(desc, dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), 0)
+        torch.cuda.synchronize()
+        assert lib.device_status() == (0, 0, 0, 0)
+        return host(dC, c0.dtype).reshape(m, n), lib.launch_count() - before
+
+    got, launches = run(a_bits, b_bits, 0)
+    assert launches == 1 and np.array_equal(got, want)
+    ra, rb, _ = lcg_buffers([m * k, n * k, 0], small=False)
+    ra_bits, rb_bits = oracle.f32_to_bf16_bits(ra.reshape(m, k)), oracle.f32_to_bf16_bits(rb.reshape(n, k))
+    in_cluster, one = run(ra_bits, rb_bits, 0)
+    two_pass, two = run(ra_bits, rb_bits, 128)
+    assert (one, two) == (1, 2) and np.array_equal(in_cluster, two_pass)
 
 
 @pytest.mark.parametrize("seed", range(3))

@@ -34,6 +34,33 @@ def test_wait_that_runs_out_is_reported_and_the_device_stays_usable(lib, gpu, ct
     assert np.array_equal(dC.cpu().numpy(), oracle.gemm_tn(a_bits, b_bits, oracle.F16))
 
 
+def test_split_summed_in_the_cluster_gives_up_cleanly(lib, gpu):
+    """The k split whose ranges are added inside a cluster (single-CTA 128-row tiles, split in two):
+    with the producer silent every CTA's waits run out, all CTAs still meet at the cluster barriers
+    around the exchange, nothing is stored, and the report comes back as usual."""
+    import torch
+    m, n, k = 512, 256, 512
+    a, b, _ = lcg_buffers([m * k, n * k, 0], small=True)
+    a_bits, b_bits = oracle.f32_to_f16_bits(a.reshape(m, k)), oracle.f32_to_f16_bits(b.reshape(n, k))
+    dA = torch.from_numpy(a_bits.view(np.int16)).cuda()
+    dB = torch.from_numpy(b_bits.view(np.int16)).cuda()
+    dC = torch.full((m, n), 7.0, device="cuda")
+    desc = lib.gemm_desc(m, n, k, lib.F16, lib.F32, cta_group=1, tile_m=128, split_k=2)
+    assert lib.gemm_plan(desc) == (1, 256, 128, 2) or lib.gemm_plan(desc)[3] == 2
+    desc.tuning[0] = 4 | 8
+    before = lib.launch_count()
+    lib.gemm_tn(desc, dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), 0)
+    assert lib.launch_count() - before == 1  # one kernel: the in-cluster form
+    with pytest.raises(lib.CuteB200Error) as e:
+        lib.synchronize()
+    assert e.value.status == lib.ERR_DEVICE_TIMEOUT and "bounded wait gave up" in e.value.message
+    assert (dC == 7.0).all().item()  # a CTA that gave up stores nothing
+    desc.tuning[0] = 0
+    lib.gemm_tn(desc, dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), 0)
+    lib.synchronize()
+    assert np.array_equal(dC.cpu().numpy(), oracle.gemm_tn(a_bits, b_bits, oracle.F16))
+
+
 def test_pusher_gives_up_with_the_other_roles(lib, gpu):
     """The several-destination form under the same knob: the pusher warp waits for
     tiles that never come, sees the CTA give up, and returns with everything else;

@@ -91,7 +91,12 @@ def test_tiling_choices_for_the_benchmark_shapes(lib):
     assert plan(16384, 1024, 8192) == (2, 256, 256, 1)
     assert plan(2048, 2048, 2048) == (1, 256, 128, 1)          # one wave of single CTAs
     assert plan(1024, 1024, 1024) == (1, 128, 128, 1)
-    assert plan(8192, 128, 8192) == (2, 128, 64, 1)            # few row tiles, long k: the 64-row pair tile, one kernel
+    assert plan(8192, 128, 8192) == (1, 128, 128, 2)           # few row tiles, long k: k cut in two, summed inside a cluster
+    assert plan(8192, 256, 8192) == (1, 256, 128, 2)
+    assert plan(1536, 1536, 2048) == (1, 128, 128, 1)          # short k: the exchange would cost more than it saves
+    desc = lib.gemm_desc(8192, 128, 8192, lib.BF16, lib.BF16)
+    desc.tuning[0] = 128                                       # without the in-cluster form: the 64-row pair tile, one kernel
+    assert lib.gemm_plan(desc) == (2, 128, 64, 1)
     assert plan(8192, 128, 8192, split_k=4)[3] == 4 and plan(8192, 128, 64, split_k=4)[3] == 1  # honoured, cut to the k blocks
     assert plan(256, 256, 256, tile_m=64)[:3] == (2, 128, 64) or plan(256, 256, 256, tile_m=64)[0] == 2
 

@@ -3,7 +3,7 @@ instantiates is clean, and each deliberate protocol bug is reported as the kind
 of error the reference's simulator reports for it (tests/diagnostics.rs)."""
 import pytest
 
-from cute_rs_b200.check import ProtocolError, check_gemm, check_signal, tiling_from_library
+from cute_rs_b200.check import ProtocolError, check_cluster_sum, check_gemm, check_signal, tiling_from_library
 
 TILINGS = [dict(cta_group=g, stages=s, mh=mh, acc_bufs=ab, kps=kps) for g, s, mh, ab, kps in
            [(2, 4, 2, 1, 1), (1, 3, 2, 1, 1), (2, 7, 1, 2, 1), (1, 4, 1, 2, 1), (2, 9, 1, 2, 1), (2, 5, 2, 2, 1), (1, 7, 1, 2, 1),
@@ -123,4 +123,23 @@ def test_completion_signal_bugs_are_reported(mutation, kind):
     kinds = (kind,) if isinstance(kind, str) else kind
     with pytest.raises(ProtocolError) as e:
         check_signal(ctas=4, chunks=3, mutations=(mutation,), seeds=range(12))
+    assert e.value.kind in kinds, str(e.value)
+
+
+# ---- the k split summed inside a cluster ---------------------------------------------------
+@pytest.mark.parametrize("kc,warps", [(2, 8), (4, 8), (2, 1)])
+def test_cluster_sum_protocol_is_clean(kc, warps):
+    check_cluster_sum(kc=kc, warps=warps)
+
+
+@pytest.mark.parametrize("mutation,kind", [
+    ("sum_before_barrier", ("race", "uninitialised")),    # partial sums of another CTA read before they are written
+    ("barrier_of_one_cta", ("race", "uninitialised")),
+    ("exit_without_barrier", ("race", "uninitialised")),  # a CTA's shared memory reused while a peer still reads it
+    ("a_warp_skips_barrier", "deadlock"),
+])
+def test_cluster_sum_bugs_are_reported(mutation, kind):
+    kinds = (kind,) if isinstance(kind, str) else kind
+    with pytest.raises(ProtocolError) as e:
+        check_cluster_sum(kc=2, warps=4, mutations=(mutation,), seeds=range(12))
     assert e.value.kind in kinds, str(e.value)
