@@ -34,6 +34,14 @@
 // ends up with its rows of the result in its own TMEM.  That halves the
 // B traffic per output.  Every CTA issues its own loads; none is shared.
 //
+// A long k with few tiles can be cut into ranges (work units): their f32 partial
+// sums are added by a second kernel through planes in global memory, or - for
+// single-CTA 128-row tiles cut in two or four - inside this kernel by the CTAs
+// of a cluster through each other's shared memory (GemmParams::kc).  Every
+// launch is a programmatic dependent of the kernel before it in the stream:
+// the set-up overlaps that kernel's tail, griddepcontrol.wait guards the
+// first global access.
+//
 // Every mbarrier wait has a time limit.  A waiter that gives up raises the
 // CTA's abort flag, writes a report to the device status word and all roles
 // fall through to the common teardown, so a protocol error ends the kernel
