@@ -476,6 +476,37 @@ def test_gemm_split_k_summed_in_the_cluster(lib, gpu, m, n, k, tile_n, split_k, 
     assert (one, two) == (1, 2) and np.array_equal(in_cluster, two_pass)
 
 
+def test_gemm_launches_of_every_form_back_to_back(lib, gpu):
+    """GEMM launches are programmatic dependents of the kernel before them, so a launch is set up while
+    its predecessor drains.  Queue the forms one behind the other without a host wait in between - pair
+    tiles, single CTAs, the 64-row tile, a k split in two kernels, a k split summed inside clusters,
+    a launch whose C is the next one's A - and check every result at the end."""
+    import torch
+    rng = np.random.default_rng(11)
+    m, n, k = 384, 256, 1024
+    a_bits = oracle.f32_to_bf16_bits(rng.integers(-4, 5, (m, k)).astype(np.float32))
+    b_bits = oracle.f32_to_bf16_bits(rng.integers(-4, 5, (n, k)).astype(np.float32))
+    b2_bits = oracle.f32_to_bf16_bits(rng.integers(-1, 2, (128, n)).astype(np.float32))  # (n2, k2 = n) for the chained product
+    want = oracle.gemm_tn(a_bits, b_bits, oracle.BF16, oracle.BF16)
+    want_chain = oracle.gemm_tn(want, b2_bits, oracle.BF16, oracle.F32)
+    dA, dB, dB2 = dev(a_bits), dev(b_bits), dev(b2_bits)
+    forms = [dict(cta_group=2, tile_m=256), dict(cta_group=1, tile_m=128, split_k=1), dict(cta_group=2, tile_m=64),
+             dict(cta_group=2, tile_m=128, split_k=2), dict(cta_group=1, tile_m=128, tile_n=128, split_k=2),
+             dict(cta_group=1, tile_m=128, split_k=4), dict()]
+    outs = [torch.zeros(m, n, dtype=torch.int16, device="cuda") for _ in forms]
+    chains = [torch.zeros(m, 128, device="cuda") for _ in forms]
+    for _ in range(4):
+        for kw, c, chain in zip(forms, outs, chains):
+            lib.gemm_tn(lib.gemm_desc(m, n, k, lib.BF16, lib.BF16, **kw), dA.data_ptr(), dB.data_ptr(), c.data_ptr(), 0)
+            # the next launch reads what this one wrote
+            lib.gemm_tn(lib.gemm_desc(m, 128, n, lib.BF16, lib.F32), c.data_ptr(), dB2.data_ptr(), chain.data_ptr(), 0)
+    torch.cuda.synchronize()
+    assert lib.device_status() == (0, 0, 0, 0)
+    for kw, c, chain in zip(forms, outs, chains):
+        assert np.array_equal(host(c, np.uint16).reshape(m, n), want), kw
+        assert np.array_equal(chain.cpu().numpy(), want_chain), kw
+
+
 @pytest.mark.parametrize("seed", range(3))
 def test_gemm_64_row_tile_random_shapes(lib, gpu, seed):
     """The 64-rows-per-CTA pair tile (tile_m = 64) over random ragged sizes, both column
