@@ -728,7 +728,8 @@ def bench_gemm_shape(lib, torch, shape, tiling, iters, pk):
     chk = BandCheck(to_bits(torch, A), to_bits(torch, B), three_bands(m), k)
     got, off = band_bits(torch, C, chk.bands)
     return {"workload": f"runtime_gemm bf16 {m}x{n}x{k} -> bf16, normal(0,0.02) seed 3", "ms": ms, "tflops": flop / ms / 1e9,
-            "kernels_per_call": launches, "torch_matmul_ms": ms_t, "ratio_to_torch": ms / ms_t,
+            "kernels_per_call": launches, "plan": dict(zip(("cta_group", "tile_n", "tile_m", "k_ranges"), lib.gemm_plan(d))),
+            "torch_matmul_ms": ms_t, "ratio_to_torch": ms / ms_t,
             "bound": "hbm" if t_hbm > t_tensor else "tensor", "roofline_ms": max(t_tensor, t_hbm),
             "frac_of_roofline": max(t_tensor, t_hbm) / ms, "algorithmic_bytes": byts, "gbs": byts / ms / 1e6,
             "parity": chk.check(got, off), "status": list(lib.device_status())}
